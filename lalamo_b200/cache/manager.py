@@ -3,10 +3,15 @@ rule, and slots for per-request state of fixed size.
 
 * Every schedule entry whose mixer declares a :class:`PagedKVNeed` gets its own key and value
   tensors ``[pages, page_size, groups, head_dim]``.  Entries with the same retention rule (all
-  keys, or a window of ``w``) form a *group*: one page pool and one block table per request serve
-  the whole group, since such layers hold the same positions.  Groups have pages of their own.
+  keys, or a window of ``w`` with the first ``f`` positions kept) form a *group*: one page pool and
+  one block table per request serve the whole group, since such layers hold the same positions.
+  Groups have pages of their own.
 * Pages are given back when a request ends, and, in a windowed group, as soon as the window has
-  passed them; they are handed out again (last freed first) without being cleared.
+  passed them (the pages of the kept first positions stay); they are handed out again (last freed
+  first) without being cleared.
+* A mixer may declare several needs at once (:class:`CompositeNeed`, nested at will): the manager
+  treats every leaf as a *cell* of its own and hands the mixer a :class:`CompositeView` of the same
+  shape.  A schedule entry with a plain need is one cell.
 * Every entry with a :class:`SlotStateNeed` gets a tensor ``[slots, *shape]``; a request holds
   one slot index for all of them, zeroed at admission by one kernel over a table of the state
   tensors (address, bytes per slot).
@@ -24,17 +29,18 @@ from dataclasses import dataclass, field
 import torch
 
 from .. import ops
-from ..parts.base import CacheNeed, CacheView, PagedKVNeed, PagedKVView, Runtime, SlotStateNeed, SlotStateView
+from ..parts.base import CacheNeed, CacheView, CompositeNeed, CompositeView, PagedKVNeed, PagedKVView, Runtime, SlotStateNeed, SlotStateView
 from .pages import OutOfPages, PagePool, SlotPool
 
-__all__ = ["CacheLayout", "CacheManager", "RequestCache", "plan_cache_layout"]
+__all__ = ["CacheLayout", "CacheManager", "RequestCache", "flatten_needs", "plan_cache_layout"]
 
 
 @dataclass
 class _Group:
     window: int | None
-    entries: list[int]  # schedule entries whose pages this group holds
+    entries: list[int]  # cells whose pages this group holds
     pool: PagePool
+    keep_first: int = 0
 
 
 @dataclass
@@ -54,10 +60,38 @@ class CacheLayout:
     group_windows: list[int | None]
     group_entries: list[list[int]]
     slot_entries: list[int]
+    group_keep_first: list[int] = field(default_factory=list)
+
+
+def flatten_needs(needs: list[CacheNeed | None], cache_from: list[int | None]) -> tuple[list[CacheNeed | None], list[int | None], list[object]]:
+    """Composite needs taken apart: ``(cells, cache_from per cell, shape per entry)``.  An entry's shape
+    is the index of its cell, or a (nested) list of such for a :class:`CompositeNeed`; an entry that reads
+    another entry's cache reads that entry's cells one by one."""
+    cells: list[CacheNeed | None] = []
+    cell_from: list[int | None] = []
+    shapes: list[object] = []
+
+    def lay(need: CacheNeed | None, source: object) -> object:
+        if isinstance(need, CompositeNeed):
+            if source is not None and (not isinstance(source, list) or len(source) != len(need.needs)):
+                raise ValueError("a schedule entry reads the cache of an entry whose mixer has other needs")
+            return [lay(part, None if source is None else source[index]) for index, part in enumerate(need.needs)]
+        if isinstance(source, list):
+            raise ValueError("a schedule entry reads the cache of an entry whose mixer has other needs")
+        cells.append(need)
+        cell_from.append(source)
+        return len(cells) - 1
+
+    for index, need in enumerate(needs):
+        source = cache_from[index]
+        shapes.append(lay(need, None if source is None else shapes[source]))
+    return cells, cell_from, shapes
 
 
 def plan_cache_layout(needs: list[CacheNeed | None], cache_from: list[int | None]) -> CacheLayout:
+    """The layout of plain needs (one cell per entry; see :func:`flatten_needs` for composite ones)."""
     windows: list[int | None] = []
+    keys: list[tuple[int | None, int]] = []
     group_entries: list[list[int]] = []
     entry_group: list[int | None] = [None] * len(needs)
     entry_owner: list[int | None] = [None] * len(needs)
@@ -71,10 +105,12 @@ def plan_cache_layout(needs: list[CacheNeed | None], cache_from: list[int | None
             entry_group[index] = entry_group[source]
             continue
         if isinstance(need, PagedKVNeed):
-            if need.window not in windows:
+            key = (need.window, need.keep_first if need.window is not None else 0)
+            if key not in keys:
+                keys.append(key)
                 windows.append(need.window)
                 group_entries.append([])
-            group = windows.index(need.window)
+            group = keys.index(key)
             group_entries[group].append(index)
             entry_group[index] = group
             entry_owner[index] = index
@@ -83,7 +119,7 @@ def plan_cache_layout(needs: list[CacheNeed | None], cache_from: list[int | None
             entry_owner[index] = index
         elif need is not None:
             raise ValueError(f"schedule entry {index}: unknown cache need {type(need).__name__}")
-    return CacheLayout(entry_group, entry_owner, windows, group_entries, slot_entries)
+    return CacheLayout(entry_group, entry_owner, windows, group_entries, slot_entries, [key[1] for key in keys])
 
 
 class CacheManager:
@@ -105,11 +141,14 @@ class CacheManager:
         self.num_pages = num_pages
         self.num_slots = num_slots
         self.runtime = runtime
+        # From here on "entry" means a cell: a schedule entry's plain need, or one leaf of its composite need.
+        self.entry_needs = needs
+        needs, cache_from, self.entry_shapes = flatten_needs(needs, cache_from)
         self.needs = needs
         self.layout = plan_cache_layout(needs, cache_from)
         self.groups = [
-            _Group(window, entries, PagePool(num_pages, name=f"group {index} (window {window})"))
-            for index, (window, entries) in enumerate(zip(self.layout.group_windows, self.layout.group_entries))
+            _Group(window, entries, PagePool(num_pages, name=f"group {index} (window {window}, first {keep} kept)"), keep)
+            for index, (window, entries, keep) in enumerate(zip(self.layout.group_windows, self.layout.group_entries, self.layout.group_keep_first))
         ]
         self.slots = SlotPool(num_slots)
         self.requests: dict[object, RequestCache] = {}
@@ -128,7 +167,7 @@ class CacheManager:
                     assert isinstance(need, PagedKVNeed)
                     # keys [page][row][group][channel]; values transposed, [page][group][channel][row]
                     self.k_pages[entry] = torch.zeros((num_pages, page_size, need.num_groups, need.head_dim), dtype=runtime.dtype, device=runtime.device)
-                    self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
+                    self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.value_dim or need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
             for entry in self.layout.slot_entries:
                 need = needs[entry]
                 assert isinstance(need, SlotStateNeed)
@@ -216,9 +255,10 @@ class CacheManager:
                 continue
             first_needed = new_length - group.window + 1  # lowest key a query at position >= new_length sees
             dead_blocks = max(0, first_needed) // self.page_size
+            kept_blocks = -(-group.keep_first // self.page_size)  # the blocks of the kept first positions stay
             blocks = record.blocks[index]
-            released = [blocks[b] for b in range(min(dead_blocks, len(blocks))) if blocks[b] >= 0]
-            for b in range(min(dead_blocks, len(blocks))):
+            released = [blocks[b] for b in range(kept_blocks, min(dead_blocks, len(blocks))) if blocks[b] >= 0]
+            for b in range(kept_blocks, min(dead_blocks, len(blocks))):
                 blocks[b] = -1
             group.pool.release(released)
             self._poison_pages(index, released)
@@ -270,6 +310,17 @@ class CacheManager:
 
     def views(self, block_tables: list[torch.Tensor], segment_slot: torch.Tensor) -> list[CacheView | None]:
         """The cache of every schedule entry for one step (``block_tables``: one device tensor per group)."""
+        cells = self._cell_views(block_tables, segment_slot)
+
+        def shape_view(shape: object) -> CacheView | None:
+            if isinstance(shape, list):
+                views = [shape_view(part) for part in shape]
+                return CompositeView(all(view is None or view.owns for view in views), views)
+            return cells[shape]
+
+        return [shape_view(shape) for shape in self.entry_shapes]
+
+    def _cell_views(self, block_tables: list[torch.Tensor], segment_slot: torch.Tensor) -> list[CacheView | None]:
         result: list[CacheView | None] = []
         for entry, owner in enumerate(self.layout.entry_owner):
             if owner is None:
@@ -288,10 +339,10 @@ class CacheManager:
         record = self.requests[request_id]
         total = 0
         for index, group in enumerate(self.groups):
-            live = record.length if group.window is None else min(record.length, group.window)
+            live = record.length if group.window is None else min(record.length, group.window + group.keep_first)
             for entry in group.entries:
-                pages = self.k_pages[entry]
-                total += 2 * live * pages.shape[2] * pages.shape[3] * pages.element_size()
+                pages, values = self.k_pages[entry], self.v_pages[entry]
+                total += live * pages.shape[2] * (pages.shape[3] + values.shape[2]) * pages.element_size()
         for state in self.states.values():
             total += state[0].numel() * state.element_size()
         return total

@@ -6,36 +6,47 @@ from .plan import (
     AttentionSpec,
     BlockSpec,
     FeedForwardSpec,
+    GatedDeltaSpec,
     GatedMLPSpec,
     MixerSpec,
     ModelPlan,
     NormSpec,
+    OutputNormBlockSpec,
+    ParallelMixerSpec,
     PositionSpec,
     RMSNormSpec,
     RopeSpec,
+    RoutedMLPSpec,
     ScheduleEntry,
     ShortConvSpec,
 )
+from .vuvulorn import VuvulornConfig
 from .registry import architectures, config_from_dict, load_config, register_architecture
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config)
+register_architecture("Vuvulorn", VuvulornConfig)
 
 __all__ = [
     "AttentionSpec",
     "BlockSpec",
     "ConfigError",
     "FeedForwardSpec",
+    "GatedDeltaSpec",
     "GatedMLPSpec",
     "Lfm2Config",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
+    "OutputNormBlockSpec",
+    "ParallelMixerSpec",
     "PositionSpec",
     "RMSNormSpec",
     "RopeSpec",
+    "RoutedMLPSpec",
     "ScheduleEntry",
     "ShortConvSpec",
     "UnknownArchitectureError",
+    "VuvulornConfig",
     "architectures",
     "config_from_dict",
     "load_config",

@@ -22,13 +22,17 @@ __all__ = [
     "EmbeddingSpec",
     "HeadSpec",
     "FeedForwardSpec",
+    "GatedDeltaSpec",
     "GatedMLPSpec",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
+    "OutputNormBlockSpec",
+    "ParallelMixerSpec",
     "PositionSpec",
     "RMSNormSpec",
     "RopeSpec",
+    "RoutedMLPSpec",
     "ScheduleEntry",
     "ShortConvSpec",
 ]
@@ -89,6 +93,42 @@ class AttentionSpec(MixerSpec):
     position: PositionSpec | None = None
     window: int | None = None
     scale: float | None = None  # None -> head_dim ** -0.5
+    value_dim: int | None = None  # size of a value head; None -> head_dim
+    keep_first: int = 0  # under a window, the first tokens of a request that stay visible (at their true positions)
+    has_bias: bool = False  # biases on the q, k, v and output projections
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec(MixerSpec):
+    """A linear-attention mixer with a matrix state per head updated by the gated delta rule,
+    ``S <- diag(g) S; S <- S + k (beta (v - S^T k))^T; o = S^T q``, one decay ``g`` per head and key
+    channel.  q, k (``num_groups`` heads of ``key_dim``) and v (``num_heads`` heads of ``value_dim``)
+    pass a causal depthwise convolution of ``conv_taps`` taps and silu; q and k are made unit vectors
+    (``x / sqrt(sum x^2 + unit_eps)``, q times ``key_dim ** -0.5``); ``beta = sigmoid(W_b h)``;
+    ``g = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias))`` through a bottleneck of ``decay_rank``; the
+    read-out is RMS-normed per head (``norm_eps``) and multiplied by ``sigmoid(W_g2 W_g1 h)`` through a
+    bottleneck of ``gate_rank``, then projected out."""
+
+    kind: ClassVar[str] = "gated_delta"
+    model_dim: int = 0
+    num_heads: int = 0
+    num_groups: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 1
+    decay_rank: int = 0
+    gate_rank: int = 0
+    norm_eps: float = 1e-6
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(MixerSpec):
+    """Several mixers side by side on the same input; the result is ``sum_i scale_i * branch_i(x)``.
+    ``branches``: ``(name, specification, scale)``; the name prefixes the branch's tensors."""
+
+    kind: ClassVar[str] = "parallel"
+    branches: tuple[tuple[str, MixerSpec, float], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -115,6 +155,37 @@ class GatedMLPSpec(FeedForwardSpec):
     model_dim: int = 0
     hidden_dim: int = 0
     activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec(FeedForwardSpec):
+    """A mixture of ``num_experts`` gated feed-forward layers of width ``hidden_dim`` of which each token
+    uses ``top``: router scores ``score(W_router h)`` in 32-bit; experts in ``group_count`` equal groups of
+    neighbours, a group scored by the sum of its two largest scores, only the best ``group_keep`` groups
+    eligible; the chosen scores (over their sum if ``renormalize``) weigh the experts' outputs."""
+
+    kind: ClassVar[str] = "routed_mlp"
+    model_dim: int = 0
+    hidden_dim: int = 0
+    num_experts: int = 0
+    top: int = 1
+    group_count: int = 1
+    group_keep: int = 1
+    score: str = "sigmoid"
+    renormalize: bool = False
+    activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class OutputNormBlockSpec:
+    """A block whose sublayers read the residual stream itself and whose norms sit on the sublayers'
+    outputs: ``x <- x + mixer_norm(mixer(x)); x <- x + ffn_norm(ffn(x))`` (``ffn=None``: no second half)."""
+
+    mixer: MixerSpec
+    mixer_norm: NormSpec
+    ffn: FeedForwardSpec | None = None
+    ffn_norm: NormSpec | None = None
+    arrangement: str = "output_norm"
 
 
 @dataclass(frozen=True)
@@ -168,7 +239,7 @@ class ScheduleEntry:
 class ModelPlan:
     vocab_size: int
     model_dim: int
-    layers: tuple[BlockSpec, ...]
+    layers: tuple[BlockSpec | OutputNormBlockSpec, ...]
     final_norm: NormSpec
     tie_embeddings: bool = True
     embedding_scale: float | None = None

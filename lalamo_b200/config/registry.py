@@ -45,19 +45,34 @@ def architectures() -> dict[str, type]:
     return dict(_ARCHITECTURES)
 
 
-def config_from_dict(raw: Mapping[str, Any]) -> ArchitectureConfig:
+def _config_type(raw: Mapping[str, Any]) -> type:
+    """The configuration class for a ``config.json``: named by the first entry of its ``architectures`` list or,
+    where it has none, by its ``architecture`` string."""
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
         raise ConfigError("architectures", "must be a non-empty list of architecture names")
     config_type = _ARCHITECTURES.get(names[0])
     if config_type is None:
         raise UnknownArchitectureError(names[0], list(_ARCHITECTURES))
-    return config_type.from_dict(raw)
+    return config_type
+
+
+def config_from_dict(raw: Mapping[str, Any]) -> ArchitectureConfig:
+    return _config_type(raw).from_dict(raw)
 
 
 def load_config(model_dir: str | Path) -> ArchitectureConfig:
+    """The typed configuration of a model folder.  A configuration class that needs more than ``config.json``
+    (sizes that only the tensors' shapes give) offers ``from_model_dir(model_dir, raw)``."""
     path = Path(model_dir) / "config.json"
     if not path.is_file():
         raise FileNotFoundError(f"{path} does not exist")
     with open(path) as stream:
-        return config_from_dict(json.load(stream))
+        raw = json.load(stream)
+    config_type = _config_type(raw)
+    from_model_dir = getattr(config_type, "from_model_dir", None)
+    if from_model_dir is not None:
+        return from_model_dir(model_dir, raw)
+    return config_type.from_dict(raw)

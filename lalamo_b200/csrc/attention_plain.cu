@@ -13,7 +13,8 @@ struct PagedLayout {
     int num_pages;
     int max_blocks;   // columns of the block table
     int num_groups;   // K/V heads
-    int head_dim;
+    int head_dim;     // channels of a query or key head
+    int value_dim;    // channels of a value head
 };
 
 // Keys are stored [page][row][group][head_dim]; values transposed, [page][group][head_dim][row], so
@@ -41,7 +42,7 @@ __device__ __forceinline__ T* value_column(T* pages, const int* block_table, con
     if (block >= layout.max_blocks) return nullptr;
     const int page = block_table[static_cast<size_t>(segment) * layout.max_blocks + block];
     if (page < 0 || page >= layout.num_pages) return nullptr;
-    const size_t base = (static_cast<size_t>(page) * layout.num_groups + group) * layout.head_dim * layout.page_size;
+    const size_t base = (static_cast<size_t>(page) * layout.num_groups + group) * layout.value_dim * layout.page_size;
     return pages + base + (position - block * layout.page_size);
 }
 
@@ -57,7 +58,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
                                           const float* __restrict__ inv_freq, int rotary_dim,
                                           const int* __restrict__ positions, const int* __restrict__ token_segment,
                                           const int* __restrict__ block_table, PagedLayout layout, int num_heads,
-                                          int write_kv, int* status) {
+                                          int write_kv, const float* __restrict__ bias, int* status) {
     // Launched to start early; once the kernel before it (the q/k/v product) is done, the attention after it
     // may start in turn and read the keys and values that this kernel does not write.
     wait_for_previous_kernel();
@@ -65,12 +66,13 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     const int token = blockIdx.x;
     const int unit = blockIdx.y;
     const int lane = threadIdx.x;
-    const int hd = layout.head_dim;
-    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int hd = layout.head_dim, vd = layout.value_dim;
+    const int width = (num_heads + layout.num_groups) * hd + layout.num_groups * vd;
     const bool is_query = unit < num_heads;
     if (!is_query && !write_kv) return;
     const int group = unit - num_heads;
     const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
+    const float* src_bias = bias ? bias + static_cast<size_t>(unit) * hd : nullptr;   // added in 32-bit, before the norm
     const float* weight = is_query ? q_weight : k_weight;
     const int position = positions[token];
 
@@ -85,15 +87,17 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
             if (lane == 0) report_error(status, kBadPage);
             return;
         }
-        const T* v_src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd;
-        for (int d = lane; d < hd; d += 32) v_dst[static_cast<size_t>(d) * layout.page_size] = v_src[d];
+        const size_t v_offset = static_cast<size_t>(num_heads + layout.num_groups) * hd + static_cast<size_t>(group) * vd;
+        const T* v_src = qkv + static_cast<size_t>(token) * width + v_offset;
+        for (int d = lane; d < vd; d += 32)
+            v_dst[static_cast<size_t>(d) * layout.page_size] = bias ? from_float<T>(to_float(v_src[d]) + bias[v_offset + d]) : v_src[d];
     }
 
     float inv = 1.0f;
     if (weight != nullptr) {
         float sum = 0.0f;
         for (int d = lane; d < hd; d += 32) {
-            const float v = to_float(src[d]);
+            const float v = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
             sum += v * v;
         }
         sum = warp_sum(sum);
@@ -101,11 +105,11 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, T* __restri
     }
     const int half = rotary_dim / 2;
     for (int d = lane; d < hd; d += 32) {
-        float y = to_float(src[d]);
+        float y = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
         if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
         if (d < rotary_dim) {
             const int partner = d < half ? d + half : d - half;
-            float other = to_float(src[partner]);
+            float other = to_float(src[partner]) + (src_bias ? src_bias[partner] : 0.0f);
             if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
             const float angle = static_cast<float>(position) * inv_freq[d < half ? d : d - half];
             float sine, cosine;
@@ -129,13 +133,13 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
                                                 const float* __restrict__ inv_freq, int rotary_dim,
                                                 const int* __restrict__ positions, const int* __restrict__ token_segment,
                                                 const int* __restrict__ block_table, PagedLayout layout, int num_heads,
-                                                int write_kv, int* status) {
+                                                int write_kv, const float* __restrict__ bias, int* status) {
     extern __shared__ float rotation[];   // cos[half], sin[half]
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int hd = layout.head_dim;
+    const int hd = layout.head_dim, vd = layout.value_dim;
     const int half = rotary_dim / 2;
-    const int width = (num_heads + 2 * layout.num_groups) * hd;
+    const int width = (num_heads + layout.num_groups) * hd + layout.num_groups * vd;
     const int position = positions[token];
     const int segment = token_segment[token];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -152,6 +156,7 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
         const bool is_query = unit < num_heads;
         const int group = unit - num_heads;
         const T* src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(unit) * hd;
+        const float* src_bias = bias ? bias + static_cast<size_t>(unit) * hd : nullptr;
         const float* weight = is_query ? q_weight : k_weight;
         T* dst;
         if (is_query) {
@@ -163,25 +168,27 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
                 if (lane == 0) report_error(status, kBadPage);
                 continue;
             }
-            const T* v_src = qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd;
-            for (int d = lane; d < hd; d += 32) v_dst[static_cast<size_t>(d) * layout.page_size] = v_src[d];
+            const size_t v_offset = static_cast<size_t>(num_heads + layout.num_groups) * hd + static_cast<size_t>(group) * vd;
+            const T* v_src = qkv + static_cast<size_t>(token) * width + v_offset;
+            for (int d = lane; d < vd; d += 32)
+                v_dst[static_cast<size_t>(d) * layout.page_size] = bias ? from_float<T>(to_float(v_src[d]) + bias[v_offset + d]) : v_src[d];
         }
         float inv = 1.0f;
         if (weight != nullptr) {
             float sum = 0.0f;
             for (int d = lane; d < hd; d += 32) {
-                const float v = to_float(src[d]);
+                const float v = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
                 sum += v * v;
             }
             sum = warp_sum(sum);
             inv = rsqrtf(sum / static_cast<float>(hd) + eps);
         }
         for (int d = lane; d < hd; d += 32) {
-            float y = to_float(src[d]);
+            float y = to_float(src[d]) + (src_bias ? src_bias[d] : 0.0f);
             if (weight != nullptr) y = round_to<T>(round_to<T>(y * inv) * round_to<T>(weight[d] + scale_offset));
             if (d < rotary_dim) {
                 const int partner = d < half ? d + half : d - half;
-                float other = to_float(src[partner]);
+                float other = to_float(src[partner]) + (src_bias ? src_bias[partner] : 0.0f);
                 if (weight != nullptr) other = round_to<T>(round_to<T>(other * inv) * round_to<T>(weight[partner] + scale_offset));
                 const int i = d < half ? d : d - half;
                 const float rotated = d < half ? -other : other;
@@ -437,16 +444,18 @@ constexpr int kPlainThreads = 128;
 constexpr int kPlainMaxDimsPerThread = 4;   // head_dim <= 512
 
 // grid (tokens, num_heads).  The query at absolute position p sees keys j with
-// max(0, p - window + 1) <= j <= p (window <= 0: all j <= p).  Scores, softmax and the
-// weighted sum of values are 32-bit.
+// max(0, p - window + 1) <= j <= p (window <= 0: all j <= p) and, under a window, the first
+// `keep_first` keys of its request besides (at their true positions).  Scores, softmax and the
+// weighted sum of values are 32-bit.  Keys are visited in chunks that start at key 0 (the kept
+// ones) and at the window's first key.
 template <typename T>
 __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                                              const T* __restrict__ v_pages, T* __restrict__ out,
                                              const int* __restrict__ positions, const int* __restrict__ token_segment,
                                              const int* __restrict__ block_table, PagedLayout layout, int num_heads,
-                                             float scale, int window, int* status) {
+                                             float scale, int window, int keep_first, int* status) {
     extern __shared__ float shared[];
-    const int hd = layout.head_dim;
+    const int hd = layout.head_dim, vd = layout.value_dim;
     float* q_shared = shared;                    // hd
     float* scores = shared + hd;                 // kPlainChunk
     float* scratch = scores + kPlainChunk;       // 33
@@ -465,8 +474,10 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
     for (int i = 0; i < kPlainMaxDimsPerThread; ++i) acc[i] = 0.0f;
     float running_max = -INFINITY, running_sum = 0.0f;
 
-    for (int chunk = first; chunk <= position; chunk += kPlainChunk) {
-        const int count = min(kPlainChunk, position - chunk + 1);
+    const int kept_end = min(keep_first, first);   // keys [0, kept_end) lie before the window and are seen all the same
+    for (int range = kept_end > 0 ? 0 : 1; range < 2; ++range)
+    for (int chunk = range == 0 ? 0 : first, end = range == 0 ? kept_end : position + 1; chunk < end; chunk += kPlainChunk) {
+        const int count = min(kPlainChunk, end - chunk);
         float local_max = -INFINITY;
         for (int i = tid; i < count; i += blockDim.x) {
             const T* k_row = page_row(const_cast<T*>(k_pages), block_table, layout, segment, chunk + i, group);
@@ -496,7 +507,7 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
 #pragma unroll
         for (int slot = 0; slot < kPlainMaxDimsPerThread; ++slot) {
             const int d = tid + slot * kPlainThreads;
-            if (d < hd) {
+            if (d < vd) {
                 float sum = acc[slot] * rescale;
                 for (int i = 0; i < count; ++i) {
                     const float p = scores[i];
@@ -510,12 +521,12 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, const T* _
         }
         __syncthreads();   // scores[] is rewritten by the next chunk
     }
-    T* dst = out + (static_cast<size_t>(token) * num_heads + head) * hd;
+    T* dst = out + (static_cast<size_t>(token) * num_heads + head) * vd;
     const float norm = running_sum > 0.0f ? 1.0f / running_sum : 0.0f;
 #pragma unroll
     for (int slot = 0; slot < kPlainMaxDimsPerThread; ++slot) {
         const int d = tid + slot * kPlainThreads;
-        if (d < hd) dst[d] = from_float<T>(acc[slot] * norm);
+        if (d < vd) dst[d] = from_float<T>(acc[slot] * norm);
     }
 }
 
@@ -527,13 +538,15 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
                           const float* k_weight, float eps, float scale_offset, const float* inv_freq, int rotary_dim,
                           const int* positions, const int* token_segment, const int* block_table, int tokens,
                           int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
-                          int write_kv, int dtype, int* status, cudaStream_t stream) {
+                          int write_kv, int dtype, int* status, cudaStream_t stream, int value_dim, const float* bias) {
     if (tokens == 0) return 0;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
-    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    if (value_dim <= 0) value_dim = head_dim;
+    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim, value_dim};
+    const bool plain_layout = value_dim == head_dim && bias == nullptr;   // what the 16-byte kernels below take
     const bool power_of_two_head = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
     const int vector_threads = (((num_heads + num_groups) * (head_dim / 8)) + 31) / 32 * 32;
-    if (tokens > 64 && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
+    if (tokens > 64 && plain_layout && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0) {
         const size_t shared = static_cast<size_t>(rotary_dim > 0 ? rotary_dim : 2) * sizeof(float);
         if (tokens >= lb::kRunKernelMinTokens) {
@@ -557,7 +570,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
             lb::qk_norm_rope_write_token_kernel<T><<<dim3(tokens, (num_heads + num_groups + lb::kTokenKernelUnits - 1) / lb::kTokenKernelUnits), 128, shared, stream>>>(
                 static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
                 k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
-                write_kv, status);
+                write_kv, bias, status);
         })
         return LB_LAUNCH_RESULT();
     }
@@ -566,7 +579,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
         lb::launch_overlapped(lb::qk_norm_rope_write_kernel<T>, grid, dim3(32), 0, stream,
             static_cast<const T*>(qkv), static_cast<T*>(q_out), static_cast<T*>(k_pages), static_cast<T*>(v_pages), q_weight,
             k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table, layout, num_heads,
-            write_kv, status);
+            write_kv, bias, status);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -574,16 +587,17 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
 int lb_paged_attention_plain(const void* q, const void* k_pages, const void* v_pages, void* out, const int* positions,
                              const int* token_segment, const int* block_table, int tokens, int num_heads,
                              int num_groups, int head_dim, int page_size, int num_pages, int max_blocks, float scale,
-                             int window, int dtype, int* status, cudaStream_t stream) {
+                             int window, int dtype, int* status, cudaStream_t stream, int value_dim, int keep_first) {
     if (tokens == 0) return 0;
-    if (head_dim > lb::kPlainThreads * lb::kPlainMaxDimsPerThread || num_heads % num_groups != 0) return -2;
-    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim};
+    if (value_dim <= 0) value_dim = head_dim;
+    if (value_dim > lb::kPlainThreads * lb::kPlainMaxDimsPerThread || num_heads % num_groups != 0 || keep_first < 0) return -2;
+    lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim, value_dim};
     const dim3 grid(tokens, num_heads);
     const size_t shared = (static_cast<size_t>(head_dim) + lb::kPlainChunk + 33) * sizeof(float);
     LB_DISPATCH_DTYPE(dtype, {
         lb::paged_attention_plain_kernel<T><<<grid, lb::kPlainThreads, shared, stream>>>(
             static_cast<const T*>(q), static_cast<const T*>(k_pages), static_cast<const T*>(v_pages), static_cast<T*>(out),
-            positions, token_segment, block_table, layout, num_heads, scale, window, status);
+            positions, token_segment, block_table, layout, num_heads, scale, window, window > 0 ? keep_first : 0, status);
     })
     return LB_LAUNCH_RESULT();
 }

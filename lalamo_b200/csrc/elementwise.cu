@@ -236,6 +236,57 @@ __global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __res
     token_ids[segment_start[segment] + segment_length[segment] - 1] = sampled[row];
 }
 
+
+// out[i] = T(x[i]): the 32-bit residual stream rounded to the activation type, for sublayers that read the
+// stream itself and not a norm of it.
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = from_float<T>(x[i]);
+}
+
+// x[r, d] = T(x[r, d] + bias[d])
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bias, int dim, size_t count) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) x[i] = from_float<T>(to_float(x[i]) + bias[i % dim]);
+}
+
+// The norm of a sublayer's output, added to the residual stream.  One block per row r:
+//   y = scale_a * (a[r] + bias_a) + scale_b * (b[r] + bias_b)        (b and the biases may be absent)
+//   residual[r] += y * rsqrt(mean(y^2) + eps) * (w + offset)
+//   rounded[r] = T(residual[r])                                      (if asked for: the next sublayer's input)
+// Sum, statistics, norm and residual sum are 32-bit.
+template <typename T>
+__global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ bias_a, float scale_a,
+                                       const T* __restrict__ b, const float* __restrict__ bias_b, float scale_b,
+                                       const float* __restrict__ weight, T* __restrict__ rounded, int dim, float eps, float scale_offset) {
+    extern __shared__ float shared[];
+    float* row_cache = shared;       // dim floats
+    float* scratch = shared + dim;   // 33 floats
+    const size_t base = static_cast<size_t>(blockIdx.x) * dim;
+    float sum = 0.0f;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        float y = to_float(a[base + d]);
+        if (bias_a) y += bias_a[d];
+        y *= scale_a;
+        if (b) {
+            float z = to_float(b[base + d]);
+            if (bias_b) z += bias_b[d];
+            y += scale_b * z;
+        }
+        row_cache[d] = y;
+        sum += y * y;
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const float h = residual[base + d] + row_cache[d] * inv * (weight[d] + scale_offset);
+        residual[base + d] = h;
+        if (rounded) rounded[base + d] = from_float<T>(h);
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -334,6 +385,42 @@ int lb_gated_activation(const void* fused, void* out, int tokens, int hidden, in
     const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
     LB_DISPATCH_DTYPE(dtype, {
         lb::gated_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(fused), static_cast<T*>(out), hidden, count, activation);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_cast_rows(const float* x, void* out, long long count, int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::cast_rows_kernel<T><<<blocks, 256, 0, stream>>>(x, static_cast<T*>(out), static_cast<size_t>(count));
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_add_bias(void* x, const float* bias, int rows, int dim, int dtype, cudaStream_t stream) {
+    const size_t count = static_cast<size_t>(rows) * dim;
+    if (count == 0) return 0;
+    const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::add_bias_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<T*>(x), bias, dim, count);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+// b, bias_a, bias_b and rounded may be null.
+int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, float scale_a, const void* b, const float* bias_b, float scale_b,
+                       const float* weight, void* rounded, int rows, int dim, float eps, float scale_offset, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
+    if (shared > 200 * 1024) return -2;
+    int threads = ((dim + 3) / 4 + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : (threads > 512 ? 512 : threads);
+    LB_DISPATCH_DTYPE(dtype, {
+        auto kernel = lb::norm_accumulate_kernel<T>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        kernel<<<rows, threads, shared, stream>>>(residual, static_cast<const T*>(a), bias_a, scale_a, static_cast<const T*>(b), bias_b, scale_b, weight,
+                                                  static_cast<T*>(rounded), dim, eps, scale_offset);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -1,0 +1,311 @@
+// The gated delta rule with one decay per head and key channel, over ragged portions of requests:
+//
+//   S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+//
+// with S a [key_dim, value_dim] matrix per request and head, kept in 32-bit in the request's state
+// slot.  Four kernels: `prepare` (short causal convolutions with silu over q, k and v, unit q and k,
+// beta and the decays, all in 32-bit), `conv_state` (the convolutions' last inputs into the slot),
+// `scan` (the recurrence, token by token) and `output` (per-head RMS norm times a sigmoid gate).
+// The order of every sum depends on the token's place in its request only, never on how the
+// request was cut into steps or on what else is in the batch.
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kPrepareMaxPerLane = 16;   // key_dim <= 512
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// The convolution's input of channel `ch` at relative time `rel` of the token's portion (negative: from the state,
+// whose rows hold relative times -(taps-1) .. -1).
+template <typename T>
+__device__ __forceinline__ float conv_input(const T* __restrict__ proj, int proj_width, const T* __restrict__ state_rows, int channels,
+                                            int start, int rel, int taps, int ch) {
+    if (rel >= 0) return to_float(proj[static_cast<size_t>(start + rel) * proj_width + ch]);
+    const int row = taps - 1 + rel;
+    return row >= 0 ? to_float(state_rows[static_cast<size_t>(row) * channels + ch]) : 0.0f;
+}
+
+// y = silu(sum_j w[ch, taps-1-j] * input(t - j)), lags in the order j = 0, 1, ...
+template <typename T>
+__device__ __forceinline__ float conv_silu(const T* __restrict__ proj, int proj_width, const T* __restrict__ state_rows, int channels,
+                                           const float* __restrict__ weight, int start, int rel, int taps, int ch) {
+    float acc = 0.0f;
+    for (int j = 0; j < taps; ++j)
+        acc += weight[static_cast<size_t>(ch) * taps + (taps - 1 - j)] * conv_input(proj, proj_width, state_rows, channels, start, rel - j, taps, ch);
+    return acc * sigmoidf_(acc);
+}
+
+// One block per token, a warp per unit: the `groups` query heads, the `groups` key heads, the `heads` value
+// heads, and per head its decays and beta.
+//   proj [tokens, proj_width]: q (groups x dk) | k (groups x dk) | v (heads x dv) | b (heads) | unused
+//   ag   [tokens, ag_width]:   a (heads x dk) | ...
+//   q_out, k_out [tokens, groups, dk], v_out [tokens, heads, dv], beta_out [tokens, heads], g_out [tokens, heads, dk]: 32-bit
+template <typename T>
+__global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, const T* __restrict__ ag, int ag_width,
+                                   const T* __restrict__ conv_state, const float* __restrict__ conv_weight,
+                                   const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                   float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
+                                   float* __restrict__ beta_out, float* __restrict__ g_out,
+                                   const int* __restrict__ token_segment, const int* __restrict__ segment_start,
+                                   const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv, int taps,
+                                   int num_slots, float unit_eps, float q_scale, int* status) {
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int segment = token_segment[token];
+    const int start = segment_start[segment];
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) {
+        if (threadIdx.x == 0) report_error(status, kBadSlot);
+        return;
+    }
+    const int channels = 2 * groups * dk + heads * dv;
+    const T* state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
+    const int rel = token - start;
+    const int units = 2 * groups + 2 * heads;
+    for (int unit = warp; unit < units; unit += warps) {
+        if (unit < 2 * groups) {
+            // a query or key head: convolution, silu, unit length (and the query's scale)
+            const bool is_query = unit < groups;
+            const int head = is_query ? unit : unit - groups;
+            const int ch0 = unit * dk;   // q channels come first, then k
+            float values[kPrepareMaxPerLane];
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kPrepareMaxPerLane; ++i) {
+                const int c = lane + 32 * i;
+                values[i] = 0.0f;
+                if (c < dk) {
+                    values[i] = conv_silu(proj, proj_width, state_rows, channels, conv_weight, start, rel, taps, ch0 + c);
+                    sum += values[i] * values[i];
+                }
+            }
+            sum = warp_sum(sum);
+            const float inv = rsqrtf(sum + unit_eps) * (is_query ? q_scale : 1.0f);
+            float* dst = (is_query ? q_out : k_out) + (static_cast<size_t>(token) * groups + head) * dk;
+#pragma unroll
+            for (int i = 0; i < kPrepareMaxPerLane; ++i) {
+                const int c = lane + 32 * i;
+                if (c < dk) dst[c] = values[i] * inv;
+            }
+        } else if (unit < 2 * groups + heads) {
+            const int head = unit - 2 * groups;
+            const int ch0 = 2 * groups * dk + head * dv;
+            float* dst = v_out + (static_cast<size_t>(token) * heads + head) * dv;
+            for (int c = lane; c < dv; c += 32) dst[c] = conv_silu(proj, proj_width, state_rows, channels, conv_weight, start, rel, taps, ch0 + c);
+        } else {
+            const int head = unit - 2 * groups - heads;
+            const float rate = expf(a_log[head]);
+            const T* a_row = ag + static_cast<size_t>(token) * ag_width + static_cast<size_t>(head) * dk;
+            float* dst = g_out + (static_cast<size_t>(token) * heads + head) * dk;
+            for (int c = lane; c < dk; c += 32) dst[c] = expf(-rate * softplusf_(to_float(a_row[c]) + dt_bias[head * dk + c]));
+            if (lane == 0) beta_out[static_cast<size_t>(token) * heads + head] = sigmoidf_(to_float(proj[static_cast<size_t>(token) * proj_width + channels + head]));
+        }
+    }
+}
+
+// One block per portion: the slot's rows become the last taps-1 inputs of [old rows ; the portion's inputs].
+// A thread walks a channel's rows upwards; row i is written after row length + i (> i) was read.
+template <typename T>
+__global__ void gdr_conv_state_kernel(const T* __restrict__ proj, int proj_width, T* __restrict__ conv_state, const int* __restrict__ segment_start,
+                                      const int* __restrict__ segment_length, const int* __restrict__ segment_slot, int channels, int taps,
+                                      int num_slots) {
+    const int segment = blockIdx.x;
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) return;   // reported by the kernel before
+    const int start = segment_start[segment], length = segment_length[segment];
+    T* rows = conv_state + static_cast<size_t>(slot) * (taps - 1) * channels;
+    for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+        for (int i = 0; i < taps - 1; ++i) {
+            const int rel = length - (taps - 1) + i;
+            rows[static_cast<size_t>(i) * channels + ch] =
+                rel >= 0 ? proj[static_cast<size_t>(start + rel) * proj_width + ch] : rows[static_cast<size_t>(taps - 1 + rel) * channels + ch];
+        }
+    }
+}
+
+// The recurrence.  grid (portions, heads, ceil(dv / 32)); a block holds 32 columns of S, each column's DKP
+// (key_dim rounded up, padded rows stay zero) rows spread over SPLIT neighbouring lanes of R = 32 rows each,
+// in registers.  Lane `part` of a column holds the rows ((i / 4) * SPLIT + part) * 4 + i % 4, so that the lanes of
+// a column read neighbouring 16-byte pieces of k, q and g from shared memory.  Tokens come in batches of 16 (8 for the
+// widest keys, whose batches would not fit the static shared memory otherwise).
+constexpr int kScanCols = 32;
+
+template <int DKP, int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT)
+gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ g, const float* __restrict__ v,
+                const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ segment_start,
+                const int* __restrict__ segment_length, const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv,
+                int num_slots, int* status) {
+    constexpr int R = DKP / SPLIT;
+    constexpr int kScanBatch = DKP > 128 ? 8 : 16;
+    static_assert(R % 4 == 0, "rows per lane come in fours");
+    __shared__ __align__(16) float k_s[kScanBatch][DKP];
+    __shared__ __align__(16) float q_s[kScanBatch][DKP];
+    __shared__ __align__(16) float g_s[kScanBatch][DKP];
+    __shared__ float v_s[kScanBatch][kScanCols];
+    __shared__ float beta_s[kScanBatch];
+    const int segment = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kScanCols;
+    const int tid = threadIdx.x, col = tid / SPLIT, part = tid % SPLIT;
+    const int group = head / (heads / groups);
+    const int slot = segment_slot[segment];
+    if (slot < 0 || slot >= num_slots) {
+        if (tid == 0) report_error(status, kBadSlot);
+        return;
+    }
+    const int start = segment_start[segment], length = segment_length[segment];
+    const int column = col0 + col;
+    const bool live = column < dv;
+    float* S_base = state + (static_cast<size_t>(slot) * heads + head) * dk * dv;
+    float S[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int row = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
+        S[i] = (live && row < dk) ? S_base[static_cast<size_t>(row) * dv + column] : 0.0f;
+    }
+    for (int t0 = 0; t0 < length; t0 += kScanBatch) {
+        const int n = min(kScanBatch, length - t0);
+        __syncthreads();   // the batch before is used up
+        for (int index = tid; index < n * DKP; index += blockDim.x) {
+            const int tt = index / DKP, c = index - tt * DKP;
+            const size_t token = static_cast<size_t>(start + t0 + tt);
+            const bool valid = c < dk;
+            k_s[tt][c] = valid ? k[(token * groups + group) * dk + c] : 0.0f;
+            q_s[tt][c] = valid ? q[(token * groups + group) * dk + c] : 0.0f;
+            g_s[tt][c] = valid ? g[(token * heads + head) * dk + c] : 1.0f;
+        }
+        for (int index = tid; index < n * kScanCols; index += blockDim.x) {
+            const int tt = index / kScanCols, c = index - tt * kScanCols;
+            const size_t token = static_cast<size_t>(start + t0 + tt);
+            v_s[tt][c] = col0 + c < dv ? v[(token * heads + head) * dv + col0 + c] : 0.0f;
+        }
+        if (tid < n) beta_s[tid] = beta[static_cast<size_t>(start + t0 + tid) * heads + head];
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float4* k4 = reinterpret_cast<const float4*>(k_s[tt]);
+            const float4* q4 = reinterpret_cast<const float4*>(q_s[tt]);
+            const float4* g4 = reinterpret_cast<const float4*>(g_s[tt]);
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < R; i += 4) {
+                const float4 decay = g4[(i >> 2) * SPLIT + part], key = k4[(i >> 2) * SPLIT + part];
+                S[i] *= decay.x;
+                S[i + 1] *= decay.y;
+                S[i + 2] *= decay.z;
+                S[i + 3] *= decay.w;
+                dot += S[i] * key.x;
+                dot += S[i + 1] * key.y;
+                dot += S[i + 2] * key.z;
+                dot += S[i + 3] * key.w;
+            }
+#pragma unroll
+            for (int offset = 1; offset < SPLIT; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            const float u = beta_s[tt] * (v_s[tt][col] - dot);
+            float o = 0.0f;
+#pragma unroll
+            for (int i = 0; i < R; i += 4) {
+                const float4 key = k4[(i >> 2) * SPLIT + part], query = q4[(i >> 2) * SPLIT + part];
+                S[i] += key.x * u;
+                S[i + 1] += key.y * u;
+                S[i + 2] += key.z * u;
+                S[i + 3] += key.w * u;
+                o += S[i] * query.x;
+                o += S[i + 1] * query.y;
+                o += S[i + 2] * query.z;
+                o += S[i + 3] * query.w;
+            }
+#pragma unroll
+            for (int offset = 1; offset < SPLIT; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+            if (part == 0 && live) out[(static_cast<size_t>(start + t0 + tt) * heads + head) * dv + column] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int row = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
+        if (live && row < dk) S_base[static_cast<size_t>(row) * dv + column] = S[i];
+    }
+}
+
+// One block per token, a warp per head: out[t, h, :] = T(o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :])).
+template <typename T>
+__global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restrict__ ag, int ag_width, int gate_offset,
+                                  const float* __restrict__ norm_weight, T* __restrict__ out, int heads, int dv, float eps) {
+    const int token = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int head = warp; head < heads; head += warps) {
+        const float* row = o + (static_cast<size_t>(token) * heads + head) * dv;
+        const T* gate = ag + static_cast<size_t>(token) * ag_width + gate_offset + static_cast<size_t>(head) * dv;
+        float sum = 0.0f;
+        for (int c = lane; c < dv; c += 32) sum += row[c] * row[c];
+        sum = warp_sum(sum);
+        const float inv = rsqrtf(sum / static_cast<float>(dv) + eps);
+        T* dst = out + (static_cast<size_t>(token) * heads + head) * dv;
+        for (int c = lane; c < dv; c += 32) dst[c] = from_float<T>(row[c] * inv * norm_weight[c] * sigmoidf_(to_float(gate[c])));
+    }
+}
+
+template <int DKP, int SPLIT>
+inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const float* k, const float* g, const float* v, const float* beta,
+                        float* state, float* out, const int* segment_start, const int* segment_length, const int* segment_slot, int heads,
+                        int groups, int dk, int dv, int num_slots, int* status) {
+    gdr_scan_kernel<DKP, SPLIT><<<grid, 32 * SPLIT, 0, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads,
+                                                                groups, dk, dv, num_slots, status);
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_width, const void* conv_state, const float* conv_weight,
+                   const float* a_log, const float* dt_bias, float* q_out, float* k_out, float* v_out, float* beta_out, float* g_out,
+                   const int* token_segment, const int* segment_start, const int* segment_slot, int tokens, int heads, int groups, int dk,
+                   int dv, int taps, int num_slots, float unit_eps, float q_scale, int dtype, int* status, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    if (dk > 32 * lb::kPrepareMaxPerLane || taps < 1 || heads % groups != 0) return -2;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::gdr_prepare_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
+                                                              static_cast<const T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
+                                                              g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
+                                                              unit_eps, q_scale, status);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_gdr_conv_state(const void* proj, int proj_width, void* conv_state, const int* segment_start, const int* segment_length,
+                      const int* segment_slot, int segments, int channels, int taps, int num_slots, int dtype, cudaStream_t stream) {
+    if (segments == 0 || taps <= 1) return 0;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::gdr_conv_state_kernel<T><<<segments, 256, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<T*>(conv_state), segment_start,
+                                                                   segment_length, segment_slot, channels, taps, num_slots);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_gdr_scan(const float* q, const float* k, const float* g, const float* v, const float* beta, float* state, float* out,
+                const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int heads, int groups, int dk, int dv,
+                int num_slots, int* status, cudaStream_t stream) {
+    if (segments == 0) return 0;
+    if (dk < 1 || dk > 256 || dv < 1 || heads % groups != 0) return -2;
+    const dim3 grid(segments, heads, (dv + lb::kScanCols - 1) / lb::kScanCols);
+    if (dk <= 32)
+        lb::launch_scan<32, 1>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+    else if (dk <= 64)
+        lb::launch_scan<64, 2>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+    else if (dk <= 128)
+        lb::launch_scan<128, 4>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+    else
+        lb::launch_scan<256, 8>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_gdr_output(const float* o, const void* ag, int ag_width, int gate_offset, const float* norm_weight, void* out, int tokens, int heads, int dv,
+                  float eps, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LB_DISPATCH_DTYPE(dtype, {
+        lb::gdr_output_kernel<T><<<tokens, 128, 0, stream>>>(o, static_cast<const T*>(ag), ag_width, gate_offset, norm_weight, static_cast<T*>(out), heads, dv, eps);
+    })
+    return LB_LAUNCH_RESULT();
+}
+
+}  // extern "C"

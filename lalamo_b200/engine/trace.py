@@ -27,7 +27,7 @@ from .executor import StepEntry
 __all__ = ["TRACE_PAGE_SIZE", "replay", "run"]
 
 TRACE_PAGE_SIZE = 16  # divides 64: a request's pages never cover more than its count rounded up to 64
-MAX_LIVE_REQUESTS = 8
+MAX_LIVE_REQUESTS = 4  # state slots: as many requests as a trace keeps live at a time
 
 
 def replay(engine: Engine, lines: Iterable[str], out_dir: Path, reply: IO[str]) -> None:

@@ -19,7 +19,7 @@ import torch
 
 from . import native
 
-__all__ = ["KernelError", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
+__all__ = ["KernelError", "ScaledSum", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
 
 
 class KernelError(RuntimeError):
@@ -45,6 +45,27 @@ class SlicedSum:
         out = torch.empty(tokens, rows, dtype=self.dtype, device=self.partials.device)
         _sum_slices(self.partials, out, "store")
         return out
+
+
+@dataclass
+class ScaledSum:
+    """A sum ``scale_0 * (tensor_0 + bias_0) + scale_1 * (tensor_1 + bias_1)`` left to its consumer
+    (:func:`norm_accumulate` computes it in 32-bit on the way): ``terms`` holds one or two
+    ``(tensor, scale, bias or None)`` of equal shape, biases 32-bit vectors over the last dimension."""
+
+    terms: list
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.terms[0][0].shape
+
+    def sum(self) -> torch.Tensor:
+        """The plain tensor, in the terms' type (32-bit arithmetic, one rounding)."""
+        total = None
+        for tensor, scale, bias in self.terms:
+            value = tensor.float() if bias is None else tensor.float() + bias
+            total = value * scale if total is None else total + value * scale
+        return total.to(self.terms[0][0].dtype)
 
 
 _ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2}
@@ -207,6 +228,58 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor | SlicedSum) -> None:
     _done(code, "residual_add")
 
 
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x`` rounded to ``out``'s type: the 32-bit residual stream as a sublayer's input."""
+    _check(x, "x", torch.float32)
+    _check(out, "out")
+    if x.shape != out.shape:
+        raise KernelError("cast_rows: shapes differ")
+    code = _lib().lb_cast_rows(_ptr(x), _ptr(out), c_longlong(x.numel()), c_int(dtype_code(out.dtype)), _stream())
+    _done(code, "cast_rows")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """``x[r, :] += bias`` in place (the sum in 32-bit, rounded to ``x``'s type)."""
+    _check(x, "x")
+    _check(bias, "bias", torch.float32)
+    if x.dim() != 2 or bias.numel() != x.shape[1]:
+        raise KernelError("add_bias: bias must have one element per column of x")
+    code = _lib().lb_add_bias(_ptr(x), _ptr(bias), c_int(x.shape[0]), c_int(x.shape[1]), c_int(dtype_code(x.dtype)), _stream())
+    _done(code, "add_bias")
+
+
+def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", weight: torch.Tensor, eps: float, *,
+                    scale_offset: float = 0.0, rounded: torch.Tensor | None = None) -> None:
+    """``residual += rms_norm(delta) * (weight + offset)`` on the 32-bit residual stream, everything in 32-bit;
+    ``delta`` may be a :class:`ScaledSum` of one or two terms, summed here.  ``rounded`` (optional, of
+    ``delta``'s type) receives the new stream rounded to that type."""
+    _check(residual, "residual", torch.float32)
+    _check(weight, "weight", torch.float32)
+    terms = delta.terms if isinstance(delta, ScaledSum) else [(delta, 1.0, None)]
+    if not 1 <= len(terms) <= 2:
+        raise KernelError("norm_accumulate: one or two terms")
+    first = terms[0][0]
+    for tensor, _, bias in terms:
+        _check(tensor, "delta", first.dtype)
+        if tensor.shape != residual.shape:
+            raise KernelError("norm_accumulate: delta and the residual stream differ in shape")
+        if bias is not None:
+            _check(bias, "bias", torch.float32)
+            if bias.numel() != residual.shape[1]:
+                raise KernelError("norm_accumulate: a bias must have one element per column")
+    if weight.numel() != residual.shape[1]:
+        raise KernelError("norm_accumulate: weight must have one element per column")
+    if rounded is not None:
+        _check(rounded, "rounded", first.dtype)
+        if rounded.shape != residual.shape:
+            raise KernelError("norm_accumulate: rounded and the residual stream differ in shape")
+    second = terms[1] if len(terms) == 2 else (None, 0.0, None)
+    code = _lib().lb_norm_accumulate(_ptr(residual), _ptr(first), _ptr(terms[0][2]), c_float(terms[0][1]), _ptr(second[0]), _ptr(second[2]), c_float(second[1]),
+                                     _ptr(weight), _ptr(rounded), c_int(residual.shape[0]), c_int(residual.shape[1]), c_float(eps), c_float(scale_offset),
+                                     c_int(dtype_code(first.dtype)), _stream())
+    _done(code, "norm_accumulate")
+
+
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     _check(src, "src")
     _check(rows, "rows", torch.int32)
@@ -261,14 +334,15 @@ def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) ->
 
 
 # ----------------------------------------------------------------------------- attention
-def _check_paged(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, num_groups: int, head_dim: int) -> tuple[int, int, int]:
+def _check_paged(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, num_groups: int, head_dim: int,
+                 value_dim: int | None = None) -> tuple[int, int, int]:
     _check(k_pages, "k_pages")
     _check(v_pages, "v_pages", k_pages.dtype)
     _check(block_table, "block_table", torch.int32)
     if k_pages.dim() != 4 or k_pages.shape[2:] != (num_groups, head_dim):
         raise KernelError("the key cache must be [pages, page_size, groups, head_dim]")
-    if v_pages.shape != (k_pages.shape[0], num_groups, head_dim, k_pages.shape[1]):
-        raise KernelError("the value cache must be [pages, groups, head_dim, page_size] (values are stored transposed)")
+    if v_pages.shape != (k_pages.shape[0], num_groups, value_dim or head_dim, k_pages.shape[1]):
+        raise KernelError("the value cache must be [pages, groups, value_dim, page_size] (values are stored transposed)")
     if block_table.dim() != 2:
         raise KernelError("block_table must be [segments, max_blocks]")
     return k_pages.shape[1], k_pages.shape[0], block_table.shape[1]
@@ -294,15 +368,24 @@ def qk_norm_rope_write(
     head_dim: int,
     write_kv: bool,
     status: torch.Tensor,
+    value_dim: int | None = None,
+    bias: torch.Tensor | None = None,
 ) -> None:
     """Splits ``qkv`` rows into heads, applies per-head norm and rotary embedding to queries and
-    keys, writes queries to ``q_out`` and keys/values into their pages."""
+    keys, writes queries to ``q_out`` and keys/values into their pages.  ``value_dim``: the size of a
+    value head where it differs from ``head_dim``; ``bias``: a 32-bit vector over ``qkv``'s columns,
+    added before the norm."""
     _check(qkv, "qkv")
     _check(q_out, "q_out", qkv.dtype)
     tokens = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + 2 * num_groups) * head_dim or q_out.numel() != tokens * num_heads * head_dim:
+    value_dim = value_dim or head_dim
+    if qkv.shape[1] != (num_heads + num_groups) * head_dim + num_groups * value_dim or q_out.numel() != tokens * num_heads * head_dim:
         raise KernelError("qk_norm_rope_write: qkv / q_out widths do not match the head counts")
-    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != qkv.shape[1]:
+            raise KernelError("qk_norm_rope_write: bias must have one element per column of qkv")
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim, value_dim)
     if k_pages.dtype != qkv.dtype:
         raise KernelError("qk_norm_rope_write: cache and activations differ in type")
     if (q_weight is None) != (k_weight is None):
@@ -324,7 +407,7 @@ def qk_norm_rope_write(
         _ptr(qkv), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(q_weight), _ptr(k_weight), c_float(eps), c_float(scale_offset),
         _ptr(inv_freq), c_int(rotary_dim), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens), c_int(num_heads),
         c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_int(1 if write_kv else 0),
-        c_int(dtype_code(qkv.dtype)), _ptr(status), _stream())
+        c_int(dtype_code(qkv.dtype)), _ptr(status), _stream(), c_int(value_dim), _ptr(bias))
     _done(code, "qk_norm_rope_write")
 
 
@@ -343,24 +426,31 @@ def paged_attention_plain(
     scale: float,
     window: int | None,
     status: torch.Tensor,
+    value_dim: int | None = None,
+    keep_first: int = 0,
 ) -> None:
-    """Causal (optionally windowed) attention of every token over its request's pages."""
+    """Causal (optionally windowed) attention of every token over its request's pages.  Under a window
+    the first ``keep_first`` keys of a request stay visible.  ``value_dim``: the size of a value head
+    (and of an output head) where it differs from ``head_dim``."""
     _check(q, "q")
     _check(out, "out", q.dtype)
     tokens = q.shape[0]
-    if q.numel() != tokens * num_heads * head_dim or out.numel() != q.numel():
+    value_dim = value_dim or head_dim
+    if q.numel() != tokens * num_heads * head_dim or out.numel() != tokens * num_heads * value_dim:
         raise KernelError("paged_attention: q / out sizes do not match the head counts")
-    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim)
+    page_size, num_pages, max_blocks = _check_paged(k_pages, v_pages, block_table, num_groups, head_dim, value_dim)
     if k_pages.dtype != q.dtype:
         raise KernelError("paged_attention: cache and queries differ in type")
-    if head_dim > 512:
-        raise KernelError(f"paged_attention: head_dim {head_dim} exceeds the supported 512")
+    if value_dim > 512:
+        raise KernelError(f"paged_attention: value_dim {value_dim} exceeds the supported 512")
+    if keep_first < 0:
+        raise KernelError("paged_attention: keep_first must not be negative")
     if num_heads % num_groups:
         raise KernelError("paged_attention: num_heads must be a multiple of num_groups")
     code = _lib().lb_paged_attention_plain(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens),
         c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
-        c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+        c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream(), c_int(value_dim), c_int(keep_first))
     _done(code, "paged_attention_plain")
 
 
@@ -598,6 +688,154 @@ def short_conv(
         _ptr(segment_slot), c_int(tokens), c_int(segments), c_int(dim), c_int(kernel_size), c_int(state.shape[0]),
         c_int(dtype_code(proj.dtype)), _ptr(status), _stream())
     _done(code, "short_conv", 2 if kernel_size > 1 else 1)
+
+
+# ---------------------------------------------------------------------- gated delta rule
+def gated_delta_rule(
+    proj: torch.Tensor,
+    low_rank: torch.Tensor,
+    conv_state: torch.Tensor | None,
+    matrix_state: torch.Tensor,
+    *,
+    conv_weight: torch.Tensor,
+    a_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    norm_weight: torch.Tensor,
+    norm_eps: float,
+    num_heads: int,
+    num_groups: int,
+    key_dim: int,
+    value_dim: int,
+    unit_eps: float,
+    token_segment: torch.Tensor,
+    segment_start: torch.Tensor,
+    segment_length: torch.Tensor,
+    segment_slot: torch.Tensor,
+    segments: int,
+    status: torch.Tensor,
+) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over the step's portions, from each
+    request's state slot and back into it.
+
+    ``proj`` ``[tokens, >= C + heads]`` holds, per token, the pre-convolution q (``groups x key_dim``), k
+    (the same) and v (``heads x value_dim``), ``C`` channels in all, then one beta logit per head;
+    ``low_rank`` ``[tokens, heads * key_dim + heads * value_dim]`` the decay logits and the output gate's
+    logits.  ``conv_weight`` is ``[C, taps]`` (last column: the current token), ``conv_state``
+    ``[slots, taps - 1, C]`` (the convolutions' last inputs, in the activation type), ``matrix_state``
+    ``[slots, heads, key_dim, value_dim]`` in 32-bit.  Returns the gated, normed read-out
+    ``[tokens, heads * value_dim]`` in the activation type."""
+    _check(proj, "proj")
+    _check(low_rank, "low_rank", proj.dtype)
+    _check(matrix_state, "matrix_state", torch.float32)
+    for name, tensor in (("conv_weight", conv_weight), ("a_log", a_log), ("dt_bias", dt_bias), ("norm_weight", norm_weight)):
+        _check(tensor, name, torch.float32)
+    for name, tensor in (("token_segment", token_segment), ("segment_start", segment_start), ("segment_length", segment_length), ("segment_slot", segment_slot)):
+        _check(tensor, name, torch.int32)
+    tokens = proj.shape[0]
+    channels = 2 * num_groups * key_dim + num_heads * value_dim
+    taps = conv_weight.shape[1]
+    if num_heads % num_groups or key_dim < 1 or key_dim > 256 or value_dim < 1:
+        raise KernelError(f"gated_delta_rule: {num_heads} heads over {num_groups} groups with key size {key_dim} (at most 256) is not supported")
+    if proj.shape[1] < channels + num_heads or low_rank.shape != (tokens, num_heads * (key_dim + value_dim)):
+        raise KernelError("gated_delta_rule: proj or low_rank is too narrow for the head counts")
+    if conv_weight.shape != (channels, taps) or a_log.numel() != num_heads or dt_bias.numel() != num_heads * key_dim or norm_weight.numel() != value_dim:
+        raise KernelError("gated_delta_rule: conv_weight, a_log, dt_bias or norm_weight has the wrong size")
+    num_slots = matrix_state.shape[0]
+    if matrix_state.shape != (num_slots, num_heads, key_dim, value_dim):
+        raise KernelError("gated_delta_rule: matrix_state must be [slots, heads, key_dim, value_dim]")
+    if taps > 1:
+        if conv_state is None:
+            raise KernelError("gated_delta_rule: a convolution of more than one tap needs its state")
+        _check(conv_state, "conv_state", proj.dtype)
+        if conv_state.shape != (num_slots, taps - 1, channels):
+            raise KernelError("gated_delta_rule: conv_state must be [slots, taps - 1, channels]")
+    device = proj.device
+    q = torch.empty(tokens, num_groups, key_dim, dtype=torch.float32, device=device)
+    k = torch.empty_like(q)
+    v = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
+    beta = torch.empty(tokens, num_heads, dtype=torch.float32, device=device)
+    decay = torch.empty(tokens, num_heads, key_dim, dtype=torch.float32, device=device)
+    lib = _lib()
+    code = lib.lb_gdr_prepare(_ptr(proj), c_int(proj.shape[1]), _ptr(low_rank), c_int(low_rank.shape[1]), _ptr(conv_state), _ptr(conv_weight), _ptr(a_log),
+                              _ptr(dt_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(token_segment), _ptr(segment_start), _ptr(segment_slot),
+                              c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(taps), c_int(num_slots),
+                              c_float(unit_eps), c_float(key_dim ** -0.5), c_int(dtype_code(proj.dtype)), _ptr(status), _stream())
+    _done(code, "gdr_prepare")
+    if taps > 1:
+        code = lib.lb_gdr_conv_state(_ptr(proj), c_int(proj.shape[1]), _ptr(conv_state), _ptr(segment_start), _ptr(segment_length), _ptr(segment_slot),
+                                     c_int(segments), c_int(channels), c_int(taps), c_int(num_slots), c_int(dtype_code(proj.dtype)), _stream())
+        _done(code, "gdr_conv_state")
+    read_out = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
+    code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(beta), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
+                           _ptr(segment_slot), c_int(segments), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(num_slots),
+                           _ptr(status), _stream())
+    _done(code, "gdr_scan")
+    out = torch.empty(tokens, num_heads * value_dim, dtype=proj.dtype, device=device)
+    code = lib.lb_gdr_output(_ptr(read_out), _ptr(low_rank), c_int(low_rank.shape[1]), c_int(num_heads * key_dim), _ptr(norm_weight), _ptr(out), c_int(tokens),
+                             c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream())
+    _done(code, "gdr_output")
+    return out
+
+
+# ------------------------------------------------------------------------ routed experts
+_ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: int = 1, group_keep: int = 1, score: str = "sigmoid",
+              renormalize: bool = False, weight_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Chooses ``top`` experts per token: 32-bit router logits ``x @ router.T``, scores (``"sigmoid"`` or
+    ``"softmax"``), only experts of the ``group_keep`` best of ``group_count`` groups of neighbours eligible
+    (a group's score: the sum of its two largest scores).  Returns ``(chosen int32 [tokens, top], weights
+    float32 [tokens, top])``, the weights being the chosen scores (over their sum if ``renormalize``) times
+    ``weight_scale``."""
+    _check(x, "x")
+    _check(router, "router", torch.float32)
+    if score not in _ROUTER_SCORES:
+        raise KernelError(f"moe_route: unknown score {score!r}; known: {sorted(_ROUTER_SCORES)}")
+    tokens, width = x.shape
+    experts = router.shape[0]
+    if router.shape[1] != width:
+        raise KernelError("moe_route: the router's width is not x's")
+    if not (1 <= top <= experts and group_count >= 1 and experts % group_count == 0 and 1 <= group_keep <= group_count):
+        raise KernelError(f"moe_route: top {top} of {experts} experts in {group_count} groups of which {group_keep} are kept is not a valid choice")
+    if 4 * (2 * experts + group_count) * 4 > 48 * 1024:
+        raise KernelError(f"moe_route: {experts} experts exceed the kernel's shared memory")
+    chosen = torch.empty(tokens, top, dtype=torch.int32, device=x.device)
+    weights = torch.empty(tokens, top, dtype=torch.float32, device=x.device)
+    code = _lib().lb_moe_route(_ptr(x), _ptr(router), _ptr(chosen), _ptr(weights), c_int(tokens), c_int(width), c_int(experts), c_int(top), c_int(group_count),
+                               c_int(group_keep), c_int(_ROUTER_SCORES[score]), c_int(1 if renormalize else 0), c_float(weight_scale),
+                               c_int(dtype_code(x.dtype)), _stream())
+    _done(code, "moe_route")
+    return chosen, weights
+
+
+def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+                activation: str = "silu") -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * down[e] (act(gate[e] x[t]) * (up[e] x[t]))`` with ``e = chosen[t, k]``;
+    ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  Every (token, expert)
+    pair streams its expert's weights; the weighted sum is 32-bit, in the order of ``k``."""
+    _check(x, "x")
+    for name, tensor in (("gate", gate), ("up", up), ("down", down)):
+        _check(tensor, name, x.dtype)
+    _check(chosen, "chosen", torch.int32)
+    _check(weights, "weights", torch.float32)
+    if activation not in _ACTIVATIONS:
+        raise KernelError(f"unknown activation {activation!r}; known: {sorted(_ACTIVATIONS)}")
+    tokens, width = x.shape
+    experts, ff = gate.shape[0], gate.shape[1]
+    top = chosen.shape[1]
+    if gate.shape != (experts, ff, width) or up.shape != gate.shape or down.shape != (experts, width, ff) or chosen.shape != (tokens, top) or weights.shape != chosen.shape:
+        raise KernelError("moe_experts: shapes of x, the experts' weights, chosen and weights do not agree")
+    if (width + ff) * 4 > 200 * 1024:
+        raise KernelError("moe_experts: width + ff exceed the kernel's shared memory")
+    pair_out = torch.empty(tokens * top, width, dtype=torch.float32, device=x.device)
+    code = _lib().lb_moe_expert_stream(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(pair_out), c_int(tokens * top), c_int(top), c_int(width),
+                                       c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
+    _done(code, "moe_expert_stream")
+    out = torch.empty(tokens, width, dtype=x.dtype, device=x.device)
+    code = _lib().lb_moe_combine(_ptr(pair_out), _ptr(weights), _ptr(out), c_int(tokens), c_int(top), c_int(width), c_int(dtype_code(x.dtype)), _stream())
+    _done(code, "moe_combine")
+    return out
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -61,8 +61,16 @@ class Attention(Mixer):
             raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_groups={spec.num_groups}")
         if spec.window is not None and spec.window < 1:
             raise ValueError(f"window must be positive, got {spec.window}")
+        if spec.keep_first < 0:
+            raise ValueError(f"keep_first must not be negative, got {spec.keep_first}")
+        self.value_dim = spec.value_dim or spec.head_dim
+        self.keep_first = spec.keep_first if spec.window is not None else 0
         self.qkv = runtime.matrix(torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0))
         self.out_proj = runtime.matrix(tensors["out_proj"])
+        # Biases are 32-bit vectors: those of q, k and v are added where the product's rows are split into heads,
+        # the output's by whoever consumes the output (`output_bias`), or here.
+        self.qkv_bias = runtime.vector(torch.cat([tensors["q_bias"], tensors["k_bias"], tensors["v_bias"]], dim=0)) if spec.has_bias else None
+        self.output_bias = runtime.vector(tensors["out_bias"]) if spec.has_bias else None
         self.q_norm = self.k_norm = None
         self.norm_eps, self.norm_offset = 0.0, 0.0
         if spec.qk_norm is not None:
@@ -83,16 +91,22 @@ class Attention(Mixer):
         decls = {
             "q_proj": TensorDecl((spec.num_heads * spec.head_dim, spec.model_dim)),
             "k_proj": TensorDecl((spec.num_groups * spec.head_dim, spec.model_dim)),
-            "v_proj": TensorDecl((spec.num_groups * spec.head_dim, spec.model_dim)),
-            "out_proj": TensorDecl((spec.model_dim, spec.num_heads * spec.head_dim)),
+            "v_proj": TensorDecl((spec.num_groups * (spec.value_dim or spec.head_dim), spec.model_dim)),
+            "out_proj": TensorDecl((spec.model_dim, spec.num_heads * (spec.value_dim or spec.head_dim))),
         }
+        if spec.has_bias:
+            decls["q_bias"] = TensorDecl((spec.num_heads * spec.head_dim,), role="vector")
+            decls["k_bias"] = TensorDecl((spec.num_groups * spec.head_dim,), role="vector")
+            decls["v_bias"] = TensorDecl((spec.num_groups * (spec.value_dim or spec.head_dim),), role="vector")
+            decls["out_bias"] = TensorDecl((spec.model_dim,), role="vector")
         if spec.qk_norm is not None:
             decls["q_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
             decls["k_norm"] = TensorDecl((spec.head_dim,), role="vector", init="ones")
         return decls
 
     def cache_need(self) -> CacheNeed | None:
-        return PagedKVNeed(num_groups=self.spec.num_groups, head_dim=self.spec.head_dim, window=self.spec.window)
+        return PagedKVNeed(num_groups=self.spec.num_groups, head_dim=self.spec.head_dim, window=self.spec.window,
+                           value_dim=self.spec.value_dim, keep_first=self.keep_first)
 
     # The kernels' work lists depend on where the portions start and how long they are, not on what
     # the cache holds, and they are the same for every attention layer.
@@ -114,12 +128,21 @@ class Attention(Mixer):
 
     can_accumulate = True
 
-    def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor | None:
+    def _project_out(self, mixed: torch.Tensor, residual: torch.Tensor | None, add_output_bias: bool = True) -> torch.Tensor | None:
+        if self.output_bias is not None:
+            out = ops.linear(mixed, self.out_proj, status=self.runtime.status)
+            if isinstance(out, ops.SlicedSum):
+                out = out.sum()
+            if add_output_bias:
+                ops.add_bias(out, self.output_bias)
+            return out
         if residual is not None:
             return ops.linear_accumulate(mixed, self.out_proj, residual, status=self.runtime.status)
         return ops.linear(mixed, self.out_proj, status=self.runtime.status)
 
-    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None,  # type: ignore[override]
+                add_output_bias: bool = True) -> torch.Tensor | None:
+        """``add_output_bias=False``: the caller adds :attr:`output_bias` to what this returns."""
         spec = self.spec
         qkv = ops.linear(x, self.qkv, status=self.runtime.status)
         queries = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
@@ -142,8 +165,10 @@ class Attention(Mixer):
             head_dim=spec.head_dim,
             write_kv=cache.owns,
             status=self.runtime.status,
+            value_dim=self.value_dim,
+            bias=self.qkv_bias,
         )
-        mixed = self.runtime.empty(step.tokens, spec.num_heads * spec.head_dim)
+        mixed = self.runtime.empty(step.tokens, spec.num_heads * self.value_dim)
         page_size = cache.k_pages.shape[1]
         common = dict(
             positions=step.positions,
@@ -156,8 +181,10 @@ class Attention(Mixer):
             window=spec.window,
             status=self.runtime.status,
         )
-        alone_ok = ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size)
-        tiles_ok = ops.prefill_attention_supported(self.runtime.dtype, spec.num_heads, spec.num_groups, spec.head_dim, page_size)
+        # The tensor-core kernels take keys and values of one size and windows without kept first keys.
+        plain_shape = self.value_dim == spec.head_dim and self.keep_first == 0
+        alone_ok = plain_shape and ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size)
+        tiles_ok = plain_shape and ops.prefill_attention_supported(self.runtime.dtype, spec.num_heads, spec.num_groups, spec.head_dim, page_size)
         if alone_ok:
             lists, host_lists = step.plan_of(self)
             num_alone, num_tiles = host_lists["alone"].size, host_lists["tiles"].size // 2
@@ -176,7 +203,7 @@ class Attention(Mixer):
                     split_tiles = shared_tile_keys(num_tiles, spec.num_heads, spec.num_groups, ops.sm_count(), step.tokens,
                                                    step.host_segment_length, step.host_segment_context) // 64
                 ops.attention_prefill(queries, cache.k_pages, cache.v_pages, mixed, tiles=lists["tiles"], num_tiles=num_tiles, split_tiles=split_tiles, **common)
-            return self._project_out(mixed, residual)
+            return self._project_out(mixed, residual, add_output_bias)
         ops.paged_attention_plain(
             queries,
             cache.k_pages,
@@ -191,5 +218,7 @@ class Attention(Mixer):
             scale=self.scale,
             window=spec.window,
             status=self.runtime.status,
+            value_dim=self.value_dim,
+            keep_first=self.keep_first,
         )
-        return self._project_out(mixed, residual)
+        return self._project_out(mixed, residual, add_output_bias)

@@ -27,6 +27,8 @@ __all__ = [
     "REPLAY_MAX_TOKENS",
     "CacheNeed",
     "CacheView",
+    "CompositeNeed",
+    "CompositeView",
     "FeedForward",
     "HostSegments",
     "Mixer",
@@ -93,11 +95,14 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class PagedKVNeed(CacheNeed):
-    """Keys and values of every past token (``window=None``) or of the last ``window`` tokens."""
+    """Keys and values of every past token (``window=None``) or of the last ``window`` tokens and the
+    first ``keep_first`` ones."""
 
     num_groups: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None  # size of a value head; None: head_dim
+    keep_first: int = 0  # under a window: the first positions of a request that are kept all the same
 
 
 @dataclass(frozen=True)
@@ -107,6 +112,14 @@ class SlotStateNeed(CacheNeed):
 
     shape: tuple[int, ...]
     dtype: torch.dtype | None = None
+
+
+@dataclass(frozen=True)
+class CompositeNeed(CacheNeed):
+    """Several needs of one mixer (a mixer of several branches, or one with states of several types);
+    its view is a :class:`CompositeView` with one view per need, in this order."""
+
+    needs: tuple[CacheNeed | None, ...]
 
 
 @dataclass
@@ -119,7 +132,7 @@ class CacheView:
 @dataclass
 class PagedKVView(CacheView):
     k_pages: torch.Tensor  # [pages, page_size, groups, head_dim]
-    v_pages: torch.Tensor  # [pages, groups, head_dim, page_size] (transposed)
+    v_pages: torch.Tensor  # [pages, groups, value_dim, page_size] (transposed)
     block_table: torch.Tensor  # int32 [segments, max_blocks], -1 where no page is held
 
 
@@ -127,6 +140,11 @@ class PagedKVView(CacheView):
 class SlotStateView(CacheView):
     state: torch.Tensor  # [slots, *shape]
     segment_slot: torch.Tensor  # int32 [segments]
+
+
+@dataclass
+class CompositeView(CacheView):
+    views: list  # one CacheView (or None) per need of the CompositeNeed
 
 
 @dataclass(frozen=True)

@@ -21,7 +21,7 @@ import torch
 
 from .base import CacheView, FeedForward, Mixer, Norm, Part, Runtime, StepInputs, TensorDecl, build_part, part_type
 
-__all__ = ["Block", "PreNormBlock", "block_tensor_decls", "block_type", "build_block", "register_arrangement"]
+__all__ = ["Block", "OutputNormBlock", "PreNormBlock", "block_tensor_decls", "block_type", "build_block", "register_arrangement"]
 
 _ARRANGEMENTS: dict[str, type["Block"]] = {}
 
@@ -103,6 +103,56 @@ class PreNormBlock(Block):
         if self.ffn.can_accumulate:
             return self.ffn.forward(normed, step, residual=residual)
         return self.ffn.forward(normed, step)
+
+
+@register_arrangement("output_norm")
+class OutputNormBlock(Block):
+    """``x <- x + mixer_norm(mixer(x)); x <- x + ffn_norm(ffn(x))``: the sublayers read the stream itself
+    (rounded to the activation type), the norms sit on their outputs.  Norm and residual sum are one
+    32-bit kernel, which also hands the new stream, rounded, to the next sublayer."""
+
+    roles = ("mixer", "mixer_norm", "ffn", "ffn_norm")
+    mixer_norm: Norm
+    ffn: FeedForward | None
+    ffn_norm: Norm | None
+
+    def forward(self, residual: torch.Tensor, pending: torch.Tensor | None, step: StepInputs, cache: CacheView | None) -> torch.Tensor | None:
+        from .. import ops
+
+        if pending is not None:
+            ops.residual_add(residual, pending)
+        runtime = self.runtime
+        if runtime.dtype == torch.float32:
+            x = residual  # the sublayers read the stream in place; what they return is added only after they have read it
+        else:
+            x = runtime.empty(*residual.shape)
+            ops.cast_rows(residual, x)
+        mixed = self.mixer.forward(x, step, cache)
+        if isinstance(mixed, ops.SlicedSum):
+            mixed = mixed.sum()
+        has_ffn = self.ffn is not None
+        rounded = x if has_ffn and x is not residual else None
+        self._accumulate(self.mixer_norm, residual, mixed, rounded)
+        if has_ffn:
+            out = self.ffn.forward(x, step)
+            if isinstance(out, ops.SlicedSum):
+                out = out.sum()
+            self._accumulate(self.ffn_norm, residual, out, None)
+        return None
+
+    @staticmethod
+    def _accumulate(norm: Norm, residual: torch.Tensor, delta: "torch.Tensor", rounded: torch.Tensor | None) -> None:
+        from .. import ops
+
+        accumulate = getattr(norm, "accumulate", None)
+        if accumulate is not None:
+            accumulate(residual, delta, rounded)
+            return
+        if isinstance(delta, ops.ScaledSum):
+            delta = delta.sum()
+        ops.residual_add(residual, norm.forward(delta))
+        if rounded is not None:
+            ops.cast_rows(residual, rounded)
 
 
 def build_block(spec: Any, tensors: Mapping[tuple[str, str], torch.Tensor], runtime: Runtime) -> Block:

@@ -71,7 +71,10 @@ class DecoderModel:
         planners: dict[object, Part] = {}
         for entry in self.plan.schedule:
             block = self.blocks[entry.layer]
-            for part in block.parts():
+            parts = list(block.parts())
+            while parts:
+                part = parts.pop(0)
+                parts.extend(getattr(part, "sub_parts", list)())   # a part made of parts (mixers side by side)
                 if type(part).plan_step is not Part.plan_step:
                     planners.setdefault(part.step_plan_key(), part)
         return list(planners.values())
@@ -88,6 +91,10 @@ class DecoderModel:
                         seen[value.data_ptr()] = value.numel() * value.element_size()
                 elif isinstance(value, (Part, Block)) and depth < 4:
                     visit(value, depth + 1)
+                elif isinstance(value, list) and depth < 4:
+                    for item in value:
+                        if isinstance(item, Part):
+                            visit(item, depth + 1)
 
         for entry in self.plan.schedule:
             visit(self.blocks[entry.layer])

@@ -52,3 +52,8 @@ class RMSNorm(Norm):
             write_back=delta is not None and rows is None,
         )
         return out
+
+    def accumulate(self, residual: torch.Tensor, delta: "torch.Tensor | ops.ScaledSum", rounded: torch.Tensor | None = None) -> None:
+        """``residual += norm(delta)`` on the 32-bit stream, the norm itself in 32-bit too (no rounding of the
+        normalised value); ``rounded`` receives the new stream in the activation type."""
+        ops.norm_accumulate(residual, delta, self.scale, self.spec.eps, scale_offset=self.spec.scale_offset, rounded=rounded)
