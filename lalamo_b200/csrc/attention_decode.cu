@@ -55,6 +55,7 @@ struct DecodeParams {
     int num_heads, num_groups, page_size, num_pages, max_blocks;
     int splits, blocks_per_split;   // in units of 16 keys
     int window;
+    int keep_first;                 // under a window: the request's first keys that stay visible (0: none)
     float scale_log2;               // scale * log2(e)
     int* status;
     // >= 0: the kernel is launched to start before the kernel before it has finished, and the newest `fresh_keys`
@@ -205,9 +206,17 @@ attention_decode_kernel(const DecodeParams p) {
     const int position = p.positions[token];
     const int segment = p.token_segment[token];
     const int first_visible = p.window > 0 ? max(0, position - p.window + 1) : 0;
-    const int first_block = first_visible / 16, last_block = position / 16;
-    const int begin = first_block + split * p.blocks_per_split;
-    const int end = min(begin + p.blocks_per_split, last_block + 1);
+    const int last_block = position / 16;
+    // The blocks a token sees, counted through: those of the kept first keys, then those from the window's first key on
+    // (one run from block 0 where the two meet).  `begin`, `end` and a warp's turns count in that list; block_of() gives
+    // the block's true number.
+    const int kept_wanted = p.window > 0 ? (p.keep_first + 15) / 16 : 0;
+    const int kept_blocks = kept_wanted < first_visible / 16 ? kept_wanted : 0;
+    const int first_block = kept_wanted < first_visible / 16 ? first_visible / 16 : (kept_wanted > 0 ? 0 : first_visible / 16);
+    const int keep_first = p.window > 0 ? p.keep_first : 0;
+    auto block_of = [&](int listed) { return listed < kept_blocks ? listed : listed - kept_blocks + first_block; };
+    const int begin = split * p.blocks_per_split;
+    const int end = min(begin + p.blocks_per_split, kept_blocks + last_block - first_block + 1);
     const int rows_here = min(16, heads_per_group - row_tile * 16);
     const int head_base = group * heads_per_group + row_tile * 16;
 
@@ -227,14 +236,14 @@ attention_decode_kernel(const DecodeParams p) {
     const DecodeLaneSources sources = decode_lane_sources<HD>(p, group, lane);
     int table_first = 0;
     int lane_in_page = 0;
-    int lane_page = lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * lane, lane_in_page) : -1;
+    int lane_page = lane < count ? decode_page_of(p, segment, block_of(begin + warp + kDecodeWarps * lane), lane_in_page) : -1;
     int issued = 0, issue_stage = 0;   // issue_stage = issued % kStages, kept by hand (the modulo costs instructions in every turn)
     // Starts the copies of this warp's next block, if there is one; a group is committed either way.
     auto issue_next = [&]() {
         if (issued < count) {
             if (issued - table_first == 32) {
                 table_first = issued;
-                lane_page = issued + lane < count ? decode_page_of(p, segment, begin + warp + kDecodeWarps * (issued + lane), lane_in_page) : -1;
+                lane_page = issued + lane < count ? decode_page_of(p, segment, block_of(begin + warp + kDecodeWarps * (issued + lane)), lane_in_page) : -1;
             }
             issue_fragments<HD>(ring + issue_stage * Ring::kStageBytes, sources, __shfl_sync(0xffffffffu, lane_page, issued - table_first),
                                 __shfl_sync(0xffffffffu, lane_in_page, issued - table_first), lane, bad);
@@ -249,7 +258,7 @@ attention_decode_kernel(const DecodeParams p) {
     if (p.fresh_keys >= 0) {
         const int first_fresh_block = max(0, position - p.fresh_keys + 1) / 16;
         for (; started < Ring::kStages; ++started) {
-            if (issued < count && begin + warp + kDecodeWarps * issued >= first_fresh_block) break;
+            if (issued < count && block_of(begin + warp + kDecodeWarps * issued) >= first_fresh_block) break;
             issue_next();
         }
         wait_for_previous_kernel();
@@ -277,7 +286,7 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll 1
     for (int index = 0; index < count; index += 2) {
         const bool two = index + 1 < count;
-        const int blocks[2] = {begin + warp + kDecodeWarps * index, begin + warp + kDecodeWarps * (index + 1)};
+        const int blocks[2] = {block_of(begin + warp + kDecodeWarps * index), block_of(begin + warp + kDecodeWarps * (index + 1))};
         const int next_stage = read_stage + 1 == Ring::kStages ? 0 : read_stage + 1;
         const unsigned char* stages[2] = {ring + read_stage * Ring::kStageBytes, ring + next_stage * Ring::kStageBytes};
         read_stage = next_stage + 1 == Ring::kStages ? 0 : next_stage + 1;
@@ -298,18 +307,20 @@ attention_decode_kernel(const DecodeParams p) {
             }
         }
         // Lane t holds keys 4t + 2b + {0, 1} of a block for rows g (s[.][b][0..1]) and g + 8 (s[.][b][2..3]).
-        // Only the first and the last block of the visible range hold keys that must not count.
+        // Only the first and the last block of the visible range, and the last block of the kept keys, hold keys that
+        // must not count.
         bool edge[2];
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
-            edge[which] = (which == 0 || two) && (blocks[which] == first_block || blocks[which] == last_block);
+            edge[which] = (which == 0 || two) && (blocks[which] == first_block || blocks[which] == last_block || blocks[which] == kept_blocks - 1 ||
+                                                   (first_block == 0 && keep_first > 0 && blocks[which] <= first_visible / 16));
             if (edge[which]) {
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int key = blocks[which] * 16 + 4 * t + 2 * b + (c & 1);
-                        if (key < first_visible || key > position) s[which][b][c] = -INFINITY;
+                        if ((key < first_visible && key >= keep_first) || key > position) s[which][b][c] = -INFINITY;
                     }
                 }
             }
@@ -372,8 +383,8 @@ attention_decode_kernel(const DecodeParams p) {
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const int low = blocks[which] * 16 + 4 * t + 2 * i, high = low + 1;
-                        mask[i] = ((low >= first_visible && low <= position) ? 0x0000ffffu : 0u) |
-                                  ((high >= first_visible && high <= position) ? 0xffff0000u : 0u);
+                        mask[i] = (((low >= first_visible || low < keep_first) && low <= position) ? 0x0000ffffu : 0u) |
+                                  (((high >= first_visible || high < keep_first) && high <= position) ? 0xffff0000u : 0u);
                     }
 #pragma unroll
                     for (int n = 0; n < HD / 8; ++n) {
@@ -536,11 +547,12 @@ long long lb_attention_decode_scratch_floats(int tokens, int num_heads, int head
 int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* scratch,
                         const int* positions, const int* token_segment, const int* block_table, const int* token_list,
                         int tokens, int num_heads, int num_groups, int head_dim, int page_size, int num_pages, int max_blocks,
-                        float scale, int window, int splits, int blocks_per_split, int fresh_keys, int* status, cudaStream_t stream) {
+                        float scale, int window, int splits, int blocks_per_split, int fresh_keys, int* status, cudaStream_t stream,
+                        int keep_first) {
     // fresh_keys >= 0: see DecodeParams (the caller's previous kernel on the stream writes at most that many of
     // the newest positions a token sees, and lets this kernel start early); -1: an ordinary launch.
     if (tokens == 0) return 0;
-    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1 || !(scale > 0.0f) || fresh_keys < -1) return -2;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || splits < 1 || blocks_per_split < 1 || !(scale > 0.0f) || fresh_keys < -1 || keep_first < 0) return -2;
     lb::DecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -560,6 +572,7 @@ int lb_attention_decode(const void* q, const void* k_pages, const void* v_pages,
     p.splits = splits;
     p.blocks_per_split = blocks_per_split;
     p.window = window;
+    p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
     p.fresh_keys = fresh_keys;
@@ -652,7 +665,7 @@ extern "C" int lb_attention_decode_static(const void* q, const void* k_pages, co
     // Every partial slot of this call is written by the first kernel before the second reads it, so
     // nothing left over from an earlier call needs clearing.
     const int code = lb_attention_decode(q, k_pages, v_pages, out, scratch, positions, token_segment, block_table, token_list, tokens, num_heads,
-                                         num_groups, head_dim, page_size, num_pages, max_blocks, scale, window, splits, blocks_per_split, -1, status, stream);
+                                         num_groups, head_dim, page_size, num_pages, max_blocks, scale, window, splits, blocks_per_split, -1, status, stream, 0);
     if (code == -2) lb::describe(error_message, error_capacity, "attention_decode_static: head_dim must be a multiple of 16 up to 128 and page_size a multiple of 16");
     else if (code != 0) lb::describe(error_message, error_capacity, "attention_decode_static: launch failed with CUDA error %lld", code);
     return code;

@@ -54,6 +54,7 @@ struct PrefillParams {
     const int* block_table;
     int num_heads, num_groups, page_size, num_pages, max_blocks;
     int window;
+    int keep_first;   // under a window: the request's first keys that stay visible (0: none)
     float scale_log2;
     int* status;
 };
@@ -80,7 +81,7 @@ __device__ __forceinline__ PrefillTileEntry prefill_lookup(const PrefillParams& 
                                                            bool& bad) {
     PrefillTileEntry entry{-1, 0};
     const int block_first = first + 16 * lane;
-    if (lane < kPrefillKeys / 16 && block_first + 15 >= needed_first && block_first <= needed_last) {
+    if (lane < kPrefillKeys / 16 && (block_first + 15 >= needed_first || block_first < p.keep_first) && block_first <= needed_last) {
         const int blocks_per_page = p.page_size / 16;
         const int block = block_first / 16, column = block / blocks_per_page;
         entry.offset = (block - column * blocks_per_page) * 16;
@@ -154,8 +155,17 @@ attention_prefill_kernel(const PrefillParams p) {
     const int segment = p.token_segment[first_token];
     const int first_position = p.positions[first_token], last_position = first_position + count - 1;
     const int first_visible = p.window > 0 ? max(0, first_position - p.window + 1) : 0;   // of the tile's first token
-    const int tile_begin = (first_visible / kPrefillKeys) * kPrefillKeys;
-    const int num_key_tiles = (last_position - tile_begin) / kPrefillKeys + 1;
+    // The 64-key tiles the CTA walks, counted through: those of the kept first keys, then those from the window's first
+    // key on (one run from key 0 where the two meet); key0_of() gives a listed tile's first key.
+    int window_begin = (first_visible / kPrefillKeys) * kPrefillKeys;
+    const int kept_wanted = (p.keep_first + kPrefillKeys - 1) / kPrefillKeys;
+    int kept_tiles = 0;
+    if (kept_wanted > 0) {
+        if (kept_wanted < window_begin / kPrefillKeys) kept_tiles = kept_wanted;
+        else window_begin = 0;
+    }
+    const int num_key_tiles = kept_tiles + (last_position - window_begin) / kPrefillKeys + 1;
+    auto key0_of = [&](int listed) { return listed < kept_tiles ? listed * kPrefillKeys : window_begin + (listed - kept_tiles) * kPrefillKeys; };
 
     // Q fragments: rows g and g + 8 of row block rb are tokens first_token + 16 rb + g (+ 8); zero past the tile's end.
     uint32_t q_frag[RB][HD / 16][4];
@@ -193,14 +203,15 @@ attention_prefill_kernel(const PrefillParams p) {
     }
     bool bad = false;
 
-    prefill_load_tile<HD>(shared, p, group, prefill_lookup(p, segment, tile_begin, first_visible, last_position, lane, bad));
-    PrefillTileEntry next_entry = prefill_lookup(p, segment, tile_begin + kPrefillKeys, first_visible, last_position, lane, bad);
+    // A tile past the list looks up nothing: its first key lies past the last position.
+    prefill_load_tile<HD>(shared, p, group, prefill_lookup(p, segment, key0_of(0), first_visible, last_position, lane, bad));
+    PrefillTileEntry next_entry = prefill_lookup(p, segment, key0_of(1), first_visible, last_position, lane, bad);
     for (int tile = 0; tile < num_key_tiles; ++tile) {
         unsigned char* stage = shared + (tile & 1) * Shared::kStageBytes;
-        const int key0 = tile_begin + tile * kPrefillKeys;
+        const int key0 = key0_of(tile);
         if (tile + 1 < num_key_tiles) {
             prefill_load_tile<HD>(shared + ((tile + 1) & 1) * Shared::kStageBytes, p, group, next_entry);
-            next_entry = prefill_lookup(p, segment, key0 + 2 * kPrefillKeys, first_visible, last_position, lane, bad);
+            next_entry = prefill_lookup(p, segment, key0_of(tile + 2), first_visible, last_position, lane, bad);
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -212,9 +223,10 @@ attention_prefill_kernel(const PrefillParams p) {
             // first visible one are nobody's business: clear their values, since a zero probability
             // does not silence a non-finite value in the product.
             const int keep_from = first_visible - key0, keep_to = last_position - key0;   // keys [from, to] of this tile are real
+            const int kept_below = p.keep_first - key0;                                    // and so are the kept first keys
             for (int index = threadIdx.x; index < HD * kPrefillKeys; index += blockDim.x) {
                 const int channel = index / kPrefillKeys, key = index - channel * kPrefillKeys;
-                if (key < keep_from || key > keep_to) *reinterpret_cast<__nv_bfloat16*>(values + channel * Shared::kValuePitch + key * 2) = __float2bfloat16_rn(0.0f);
+                if ((key < keep_from && key >= kept_below) || key > keep_to) *reinterpret_cast<__nv_bfloat16*>(values + channel * Shared::kValuePitch + key * 2) = __float2bfloat16_rn(0.0f);
             }
             __syncthreads();
         }
@@ -262,7 +274,7 @@ attention_prefill_kernel(const PrefillParams p) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int key = key0 + (n >> 1) * 16 + 4 * t + 2 * (n & 1) + (c & 1);
-                        if (key < row_first[rb][c >> 1] || key > row_position[rb][c >> 1]) s[rb][n][c] = -INFINITY;
+                        if ((key < row_first[rb][c >> 1] && key >= p.keep_first) || key > row_position[rb][c >> 1]) s[rb][n][c] = -INFINITY;
                     }
                 }
             }
@@ -388,9 +400,9 @@ extern "C" {
 int lb_attention_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles,
                          const int* positions, const int* token_segment, const int* block_table, int num_heads,
                          int num_groups, int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window,
-                         int* status, cudaStream_t stream) {
+                         int* status, cudaStream_t stream, int keep_first) {
     if (num_tiles == 0) return 0;
-    if (page_size % 16 != 0 || num_heads % num_groups != 0 || !(scale > 0.0f)) return -2;
+    if (page_size % 16 != 0 || num_heads % num_groups != 0 || !(scale > 0.0f) || keep_first < 0) return -2;
     lb::PrefillParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -406,6 +418,7 @@ int lb_attention_prefill(const void* q, const void* k_pages, const void* v_pages
     p.num_pages = num_pages;
     p.max_blocks = max_blocks;
     p.window = window;
+    p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
     switch (head_dim) {

@@ -39,6 +39,7 @@ struct TaParams {
     const int* block_table;
     int num_heads, num_groups, tokens_per_cta;
     int page_size, num_pages, max_blocks, window;
+    int keep_first;   // under a window: the request's first keys that stay visible (0: none)
     int page_shift;   // log2 of page_size if that is a power of two, else -1
     int split_tiles;  // > 0: the grid is pairs of CTAs (a cluster of two per tile record); a tile with at least this many key tiles is shared by its pair
     float scale_log2;
@@ -164,15 +165,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int segment = p.token_segment[first_token];
     const int first_position = p.positions[first_token], last_position = first_position + count - 1;
     const int first_visible = p.window > 0 ? max(0, first_position - p.window + 1) : 0;   // of the tile's first token
-    int tile_begin = (first_visible / kTaKeys) * kTaKeys;
-    int num_key_tiles = (last_position - tile_begin) / kTaKeys + 1;
+    // The 64-key tiles the CTA walks, counted through: those of the kept first keys, then those from the window's first
+    // key on (one run from key 0 where the two meet); key0_of() gives the first key of the CTA's tile-th tile.
+    int window_begin = (first_visible / kTaKeys) * kTaKeys;
+    const int kept_wanted = (p.keep_first + kTaKeys - 1) / kTaKeys;
+    int kept_tiles = 0;
+    if (kept_wanted > 0) {
+        if (kept_wanted < window_begin / kTaKeys) kept_tiles = kept_wanted;
+        else window_begin = 0;
+    }
+    int num_key_tiles = kept_tiles + (last_position - window_begin) / kTaKeys + 1;
+    int first_listed = 0;
     const bool shared_tile = paired && num_key_tiles >= p.split_tiles;
     if (paired && !shared_tile && rank == 1) return;   // CTA 0 does this tile alone and uses no cluster barrier
     if (shared_tile) {
         const int lower = num_key_tiles / 2;
-        if (rank == 1) tile_begin += lower * kTaKeys;
+        if (rank == 1) first_listed = lower;
         num_key_tiles = rank == 0 ? lower : num_key_tiles - lower;
     }
+    auto key0_of = [&](int tile) {
+        const int listed = first_listed + tile;
+        return listed < kept_tiles ? listed * kTaKeys : window_begin + (listed - kept_tiles) * kTaKeys;
+    };
 
     if (threadIdx.x == 0) {
         barrier_init(q_full, 1);
@@ -215,8 +229,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         auto look_up = [&](int tile, int& page, int& offset) {
             page = -1;
             offset = 0;
-            const int block_first = tile_begin + tile * kTaKeys + 16 * lane;
-            if (lane < 4 && tile < num_key_tiles && block_first + 15 >= first_visible && block_first <= last_position) {
+            const int block_first = key0_of(tile) + 16 * lane;
+            if (lane < 4 && tile < num_key_tiles && (block_first + 15 >= first_visible || block_first < p.keep_first) && block_first <= last_position) {
                 const int column = p.page_shift >= 0 ? block_first >> p.page_shift : block_first / p.page_size;
                 const int entry = column < p.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.max_blocks + column] : -1;
                 if (entry >= 0 && entry < p.num_pages) {
@@ -318,7 +332,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         };
         for (int tile = 0; tile < num_key_tiles; ++tile) {
             const int s = tile & 1;
-            const int key0 = tile_begin + tile * kTaKeys;
+            const int key0 = key0_of(tile);
             if (!wait_together(s_ready, tile & 1)) {
                 ok = false;
                 break;
@@ -346,7 +360,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                             pair[e] = __uint_as_float(raw[i + e]);
                             if constexpr (kMasked) {
                                 const int key = key0 + 32 * half + i + e;
-                                if (key < row_first || key > row_position) pair[e] = -INFINITY;
+                                if ((key < row_first && key >= p.keep_first) || key > row_position) pair[e] = -INFINITY;
                             }
                         }
                         tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], pair[0], pair[1]);   // one instruction for two scores
@@ -410,7 +424,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                                     const int index = 8 * chunk + 2 * i + e;
                                     float score = __uint_as_float(raw[index]);
                                     const int key = key0 + 32 * half + index;
-                                    if (key < row_first || key > row_position) score = -INFINITY;
+                                    if ((key < row_first && key >= p.keep_first) || key > row_position) score = -INFINITY;
                                     terms[e] = exp2_hardware(fmaf(score, p.scale_log2, -shift));
                                 }
                                 partials[i] += terms[0] + terms[1];
@@ -453,7 +467,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 const int channel = row & 63, key_half = row >> 6;
                 for (int i = 0; i < 32; ++i) {
                     const int local_key = 32 * key_half + i, key = key0 + local_key;
-                    if (key < first_visible || key > last_position) {
+                    if ((key < first_visible && key >= p.keep_first) || key > last_position) {
                         const int block = local_key >> 4, in_block = local_key & 15;
                         // 32-byte swizzle: the 16-byte half of a 32-byte row is flipped in rows 4-7 of every 8
                         unsigned char* address = values + block * 2048 + channel * 32 + ((((in_block >> 3) ^ (channel >> 2)) & 1) << 4) + (in_block & 7) * 2;
@@ -567,11 +581,11 @@ extern "C" {
 int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out, const int* tiles, int num_tiles, int tokens,
                                  const int* positions, const int* token_segment, const int* block_table, int num_heads, int num_groups,
                                  int head_dim, int page_size, int num_pages, int max_blocks, float scale, int window, int split_tiles, int* status,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, int keep_first) {
     // split_tiles > 0: a pair of CTAs per tile record; a tile that sees at least that many tiles of 64 keys is
     // shared by its pair (for launches of few tiles, which the longest tile's chain of keys bounds).
     if (num_tiles == 0 || tokens == 0) return 0;
-    if (split_tiles < 0 || split_tiles == 1) return -2;
+    if (split_tiles < 0 || split_tiles == 1 || keep_first < 0) return -2;
     if (head_dim != lb::kTaHeadDim || page_size % 16 != 0 || num_groups < 1 || num_heads % num_groups != 0 || num_heads / num_groups > lb::kTaRows ||
         !(scale > 0.0f))
         return -2;
@@ -594,6 +608,7 @@ int lb_attention_prefill_tcgen05(const void* q, const void* k_pages, const void*
     p.num_pages = num_pages;
     p.max_blocks = max_blocks;
     p.window = window;
+    p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
 

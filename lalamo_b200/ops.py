@@ -481,7 +481,7 @@ def decode_attention_supported(dtype: torch.dtype, head_dim: int, page_size: int
 
 
 def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_context: int, window: int | None, head_dim: int = 64,
-                          resident_ctas: int | None = None) -> tuple[int, int]:
+                          resident_ctas: int | None = None, keep_first: int = 0) -> tuple[int, int]:
     """``(splits, blocks_per_split)`` in 16-key blocks.  Depends on the batch's size and longest
     context only.  The grid has ``splits * pairs`` CTAs of four warps, of which the device holds
     ``resident_ctas`` to a round (default: its multiprocessors times three quarters of the CTAs each
@@ -491,6 +491,8 @@ def decode_attention_plan(tokens: int, num_heads: int, num_groups: int, max_cont
     makes the fewest rounds' worth of that is taken, with at least eight blocks to a split."""
     span = min(max_context, window + 15) if window else max_context
     blocks_total = span // 16 + 1
+    if window and keep_first:
+        blocks_total = min(max_context // 16 + 1, blocks_total + -(-keep_first // 16))  # the blocks of the kept first keys come before the window's
     pairs = max(1, tokens * num_groups * -(-(num_heads // num_groups) // 16))
     slots = resident_ctas if resident_ctas is not None else sm_count() * ((3 * decode_ctas_per_sm(head_dim) + 2) // 4)
     best, best_cost = 1, None
@@ -523,8 +525,10 @@ def attention_decode(
     token_list: torch.Tensor | None = None,
     num_listed: int | None = None,
     fresh_keys: int | None = None,
+    keep_first: int = 0,
 ) -> None:
-    """Split-key tensor-core attention for tokens that attend alone (bfloat16 only).  ``max_context``
+    """Split-key tensor-core attention for tokens that attend alone (bfloat16 only).  Under a window the
+    first ``keep_first`` keys of a request stay visible.  ``max_context``
     is the largest position + 1 in the batch; it sizes the grid.  ``token_list`` (its first
     ``num_listed`` entries) restricts the call to some tokens of the batch.  ``fresh_keys``: the kernel
     launched just before on this stream is :func:`qk_norm_rope_write` (which lets its successor start
@@ -547,7 +551,8 @@ def attention_decode(
         raise KernelError(f"attention_decode: head_dim {head_dim} (supported: {DECODE_HEAD_DIMS}) or page_size {page_size} (a multiple of 16) is not supported")
     if num_heads % num_groups:
         raise KernelError("attention_decode: num_heads must be a multiple of num_groups")
-    splits, blocks_per_split = decode_attention_plan(tokens, num_heads, num_groups, max_context, window, head_dim)
+    keep_first = keep_first if window else 0
+    splits, blocks_per_split = decode_attention_plan(tokens, num_heads, num_groups, max_context, window, head_dim, keep_first=keep_first)
     needed = tokens * num_heads * splits * (head_dim + 2)
     if scratch is None:
         scratch = torch.empty(needed, dtype=torch.float32, device=q.device)
@@ -559,7 +564,7 @@ def attention_decode(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(positions), _ptr(token_segment), _ptr(block_table),
         _ptr(token_list), c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
         c_float(scale), c_int(window if window else 0), c_int(splits), c_int(blocks_per_split), c_int(-1 if fresh_keys is None else fresh_keys),
-        _ptr(status), _stream())
+        _ptr(status), _stream(), c_int(keep_first))
     _done(code, "attention_decode", 2 if splits > 1 else 1)   # the kernel and the merge of its splits
 
 
@@ -592,8 +597,10 @@ def attention_prefill(
     status: torch.Tensor,
     kernel: str | None = None,
     split_tiles: int = 0,
+    keep_first: int = 0,
 ) -> None:
-    """Tensor-core attention for portions of prompts (bfloat16 only).  ``tiles`` is ``[num_tiles, 2]``:
+    """Tensor-core attention for portions of prompts (bfloat16 only).  Under a window the first
+    ``keep_first`` keys of a request stay visible.  ``tiles`` is ``[num_tiles, 2]``:
     first token and count (at most 32) of runs of consecutive tokens of one request.  Head size 64 runs
     on the tcgen05 kernel (scores and output in tensor memory), the other sizes on the ``mma.sync``
     one; ``kernel="mma"`` or ``"tcgen05"`` forces one of them.  ``split_tiles`` > 1 (tcgen05 kernel only):
@@ -619,7 +626,7 @@ def attention_prefill(
         code = _lib().lb_attention_prefill_tcgen05(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), c_int(q.shape[0]), _ptr(positions), _ptr(token_segment),
             _ptr(block_table), c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks),
-            c_float(scale), c_int(window if window else 0), c_int(split_tiles), _ptr(status), _stream())
+            c_float(scale), c_int(window if window else 0), c_int(split_tiles), _ptr(status), _stream(), c_int(keep_first if window else 0))
         if code == -5:
             raise KernelError("attention_prefill: the driver made no tensor map for these tensors")
         _done(code, "attention_prefill (tcgen05)")
@@ -627,7 +634,7 @@ def attention_prefill(
     code = _lib().lb_attention_prefill(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(tiles), c_int(num_tiles), _ptr(positions), _ptr(token_segment), _ptr(block_table),
         c_int(num_heads), c_int(num_groups), c_int(head_dim), c_int(page_size), c_int(num_pages), c_int(max_blocks), c_float(scale),
-        c_int(window if window else 0), _ptr(status), _stream())
+        c_int(window if window else 0), _ptr(status), _stream(), c_int(keep_first if window else 0))
     _done(code, "attention_prefill")
 
 

@@ -179,10 +179,11 @@ class Attention(Mixer):
             head_dim=spec.head_dim,
             scale=self.scale,
             window=spec.window,
+            keep_first=self.keep_first,
             status=self.runtime.status,
         )
-        # The tensor-core kernels take keys and values of one size and windows without kept first keys.
-        plain_shape = self.value_dim == spec.head_dim and self.keep_first == 0
+        # The tensor-core kernels take keys and values of one size.
+        plain_shape = self.value_dim == spec.head_dim
         alone_ok = plain_shape and ops.decode_attention_supported(self.runtime.dtype, spec.head_dim, page_size)
         tiles_ok = plain_shape and ops.prefill_attention_supported(self.runtime.dtype, spec.num_heads, spec.num_groups, spec.head_dim, page_size)
         if alone_ok:

@@ -265,6 +265,47 @@ def test_attention_edges_with_one_key_that_stands_out(dim, vdim, dtype):
         assert np.abs(got - want).max() < (1e-3 if dtype == torch.float32 else 0.5), (keep_first, special)
 
 
+@pytest.mark.parametrize("kernel", ["alone", "tiles-mma", "tiles-tcgen05", "tiles-tcgen05-pairs"])
+@pytest.mark.parametrize("dim", [64, 32])
+@pytest.mark.parametrize("window,keep_first,special", [(37, 5, 4), (37, 5, 5), (37, 16, 15), (37, 17, 16), (37, 0, 100), (100, 70, 69), (100, 64, 64), (20, 130, 129),
+                                                       (64, 1, 0), (1, 3, 2), (300, 40, 39)])
+def test_tensor_core_attention_with_kept_first_keys(window, keep_first, special, dim, kernel):
+    """Every position of a 400-token request as a query, on each of the tensor-core kernels: tokens that attend alone
+    (keys split over CTAs) and tiles of consecutive tokens; one key stands out wherever it is seen."""
+    from lalamo_b200 import ops
+
+    if kernel.startswith("tiles-tcgen05") and dim != 64:
+        pytest.skip("the tcgen05 attention takes head size 64")
+    generator = np.random.default_rng(window + keep_first + special)
+    n, heads, groups, page_size, dtype = 400, 4, 2, 16, torch.bfloat16
+    keys = 0.3 * generator.standard_normal((n, groups, dim))
+    values = generator.standard_normal((n, groups, dim))
+    direction = generator.standard_normal(dim)
+    direction /= np.linalg.norm(direction)
+    keys[special] = 6.0 * direction
+    values[special] = 50.0
+    q = 0.3 * generator.standard_normal((n, heads, dim)) + 4.0 * direction
+    keys, values, q = (torch.from_numpy(a).to(dtype).double().numpy() for a in (keys, values, q))
+    positions = list(range(n))
+    want = plain_masked_attention(q, keys, values, positions, 0.5, window, keep_first)
+    k_pages, v_pages, table = paged(keys, values, page_size, dtype, special)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(n, heads * dim, dtype=dtype, device="cuda")
+    common = dict(positions=torch.arange(n, dtype=torch.int32, device="cuda"), token_segment=torch.zeros(n, dtype=torch.int32, device="cuda"), block_table=table,
+                  num_heads=heads, num_groups=groups, head_dim=dim, scale=0.5, window=window, status=status, keep_first=keep_first)
+    queries = torch.from_numpy(q).to(dtype).cuda().reshape(n, -1).contiguous()
+    if kernel == "alone":
+        ops.attention_decode(queries, k_pages, v_pages, out, max_context=n, **common)
+    else:
+        tiles = torch.tensor([[first, min(32, n - first)] for first in range(0, n, 32)], dtype=torch.int32, device="cuda").reshape(-1)
+        ops.attention_prefill(queries, k_pages, v_pages, out, tiles=tiles, num_tiles=tiles.numel() // 2, kernel="mma" if kernel == "tiles-mma" else "tcgen05",
+                              split_tiles=2 if kernel.endswith("pairs") else 0, **common)
+    got = out.float().cpu().numpy().reshape(want.shape)
+    assert int(status.item()) == 0
+    worst = np.abs(got - want).max(axis=(1, 2))
+    assert worst.max() < 0.5, (int(worst.argmax()), float(worst.max()))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,groups,dk,dv,taps", [(2, 1, 16, 32, 3), (3, 3, 40, 24, 1), (2, 2, 72, 16, 4), (4, 2, 128, 64, 2), (1, 1, 160, 40, 3)])
 def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, dv, taps, dtype):
