@@ -223,7 +223,8 @@ def time_prefill(engine, config, tokens: int, steps: int, warmup: int) -> dict:
         if iteration >= warmup:
             times.append(begin.elapsed_time(end))
     milliseconds = statistics.median(times)
-    return {"ms": milliseconds, "tokens": tokens, "value": tokens / (milliseconds / 1e3), "flops": prompt_flops(config, tokens)}
+    flops = prompt_flops(config, tokens) if hasattr(config, "hidden_size") else plan_flops(config.to_plan(), tokens)
+    return {"ms": milliseconds, "tokens": tokens, "value": tokens / (milliseconds / 1e3), "flops": flops}
 
 
 def time_prompts(model, config, count: int, tokens: int, rounds: int = 2, max_batch_tokens: int | None = None) -> dict:
@@ -300,6 +301,93 @@ def shape_record(config, preset: str) -> dict:
             "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads, "head_dim": config.head_dim, "ffn": config.ffn_dim,
             "vocab": config.vocab_size, "conv_taps": config.conv_kernel_size,
             "attention_layers": sum(kind == "full_attention" for kind in config.layer_types)}
+
+
+def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
+    """Floating-point operations of reading a prompt of `tokens` tokens whole, from a model's plan: every product of every
+    layer (of a routed feed-forward the router and the experts a token uses), attention (a multiply-add per query, visible
+    key and channel, for scores and for values, under the window if there is one), the delta rule's three passes over a
+    head's state per token, and the read-out of the wanted rows."""
+    from lalamo_b200.config import AttentionSpec, GatedDeltaSpec, GatedMLPSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
+
+    def mixer_flops(spec) -> float:
+        if isinstance(spec, ParallelMixerSpec):
+            return sum(mixer_flops(branch) for _, branch, _ in spec.branches)
+        if isinstance(spec, AttentionSpec):
+            value_dim = spec.value_dim or spec.head_dim
+            rows = (spec.num_heads + spec.num_groups) * spec.head_dim + spec.num_groups * value_dim + spec.num_heads * value_dim
+            window = spec.window or tokens
+            pairs = sum(min(position + 1, window + spec.keep_first) for position in range(tokens))
+            return 2.0 * rows * spec.model_dim * tokens + 2.0 * spec.num_heads * (spec.head_dim + value_dim) * pairs
+        if isinstance(spec, GatedDeltaSpec):
+            inner = spec.num_heads * (spec.key_dim + spec.value_dim)
+            rows = 2 * spec.num_groups * spec.key_dim + 2 * spec.num_heads * spec.value_dim + spec.num_heads + spec.decay_rank + spec.gate_rank
+            per_token = 2.0 * rows * spec.model_dim + 2.0 * inner * max(spec.decay_rank, spec.gate_rank) + 8.0 * spec.num_heads * spec.key_dim * spec.value_dim
+            return per_token * tokens
+        if isinstance(spec, ShortConvSpec):
+            return 2.0 * 4 * spec.model_dim * spec.model_dim * tokens
+        raise TypeError(f"no operation count for {type(spec).__name__}")
+
+    def ffn_flops(spec) -> float:
+        if spec is None:
+            return 0.0
+        if isinstance(spec, GatedMLPSpec):
+            return 2.0 * 3 * spec.model_dim * spec.hidden_dim * tokens
+        if isinstance(spec, RoutedMLPSpec):
+            return 2.0 * (3 * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens
+        raise TypeError(f"no operation count for {type(spec).__name__}")
+
+    total = 2.0 * plan.model_dim * plan.vocab_size * wanted_rows
+    for entry in plan.schedule:
+        layer = plan.layers[entry.layer]
+        total += mixer_flops(layer.mixer) + ffn_flops(layer.ffn)
+    return total
+
+
+def run_compare(arguments, peaks: dict, peak_source: str) -> int:
+    """`--config vuvulorn-compare`: the Vuvulorn shapes beside the LFM2 shapes of the same width and depth (random weights):
+    a prompt of 2,048 tokens in one step, and decode steps at batch 8 and 64 with 4,096 tokens behind every request."""
+    import torch
+
+    from lalamo_b200.config import config_from_dict
+    from lalamo_b200.engine import Engine, EngineConfig
+    from lalamo_b200.model_registry import PRESETS
+
+    peak_flops = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+    steps, warmup = max(20, min(arguments.steps, 100)), max(arguments.warmup, 3)
+    context, prompt = arguments.context, 2048
+    clocks = ClockSampler()
+    clocks.start()
+    rows = []
+    for size in arguments.compare_sizes.split(","):
+        record = {"size": size}
+        for family in ("vuvulorn", "lfm2"):
+            preset = f"{family}-{size}"
+            config = config_from_dict(PRESETS[preset])
+            engine = Engine.random(config, seed=7, std=0.02, engine_config=EngineConfig(
+                dtype="bfloat16", page_size=16, max_tokens=64 * (context + 64), max_requests=64, max_batch_tokens=prompt))
+            torch.cuda.empty_cache()
+            fill_cache_randomly(engine, torch.Generator(device="cuda").manual_seed(3))
+            plan = config.to_plan()
+            measured = time_prefill(engine, config, prompt, steps=5, warmup=3)
+            flops = plan_flops(plan, prompt)
+            arm = {"prefill_tokens_per_s": round(measured["value"], 1), "prefill_ms": round(measured["ms"], 3), "prefill_tflops": round(flops / measured["ms"] / 1e9, 1),
+                   "prefill_frac_of_gemm_peak": round(flops / (measured["ms"] / 1e3) / (peak_flops * 1e12), 4)}
+            for batch in (8, 64):
+                decode = time_decode(engine, batch, context, steps, warmup)
+                arm[f"decode_b{batch}_tokens_per_s"] = round(decode["tokens_per_s_median"], 1)
+                arm[f"decode_b{batch}_ms"] = round(decode["ms_median"], 4)
+                arm[f"decode_b{batch}_gb"] = round(decode["bytes_per_step"] / 1e9, 3)
+                arm[f"decode_b{batch}_frac_of_copy_bandwidth"] = round(decode["bytes_per_step"] / (decode["ms_median"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+                arm[f"decode_b{batch}_launches_per_step"] = decode["launches"] // steps
+            record[family] = arm
+            del engine
+            torch.cuda.empty_cache()
+        rows.append(record)
+    print(json.dumps({"config": "vuvulorn-compare", "prompt_tokens": prompt, "context": context, "dtype": "bf16",
+                      "data": "synthetic: random bf16 weights N(0,0.02), random token ids, random cache contents", "peaks": peak_source,
+                      "sizes": rows, "clocks": clocks.stop()}))
+    return 0
 
 
 def run_mixed(arguments, peaks: dict, peak_source: str) -> int:
@@ -439,7 +527,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long"],
+    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare measures")
+    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare"],
                         help="lfm2-1.2b-decode (default): the decode step and its points; lfm2-350m-mixed: 64 requests with prompts of 128 to 2,048 "
                              "tokens and 256 new tokens through the scheduler; lfm2-700m-long: 16,384-token prompts at batch 1 and 8, then 512 decode steps")
     parser.add_argument("--batch", type=int, default=8)
@@ -476,6 +565,8 @@ def main() -> int:
         return run_mixed(arguments, peaks, peak_source)
     if arguments.config == "lfm2-700m-long":
         return run_long(arguments, peaks, peak_source)
+    if arguments.config == "vuvulorn-compare":
+        return run_compare(arguments, peaks, peak_source)
     if arguments.requests:
         requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
         engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)

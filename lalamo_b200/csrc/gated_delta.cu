@@ -105,7 +105,7 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
     }
 }
 
-// One block per portion: the slot's rows become the last taps-1 inputs of [old rows ; the portion's inputs].
+// grid (portions, channel slices): the slot's rows become the last taps-1 inputs of [old rows ; the portion's inputs].
 // A thread walks a channel's rows upwards; row i is written after row length + i (> i) was read.
 template <typename T>
 __global__ void gdr_conv_state_kernel(const T* __restrict__ proj, int proj_width, T* __restrict__ conv_state, const int* __restrict__ segment_start,
@@ -116,7 +116,7 @@ __global__ void gdr_conv_state_kernel(const T* __restrict__ proj, int proj_width
     if (slot < 0 || slot >= num_slots) return;   // reported by the kernel before
     const int start = segment_start[segment], length = segment_length[segment];
     T* rows = conv_state + static_cast<size_t>(slot) * (taps - 1) * channels;
-    for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
         for (int i = 0; i < taps - 1; ++i) {
             const int rel = length - (taps - 1) + i;
             rows[static_cast<size_t>(i) * channels + ch] =
@@ -128,9 +128,27 @@ __global__ void gdr_conv_state_kernel(const T* __restrict__ proj, int proj_width
 // The recurrence.  grid (portions, heads, ceil(dv / 32)); a block holds 32 columns of S, each column's DKP
 // (key_dim rounded up, padded rows stay zero) rows spread over SPLIT neighbouring lanes of R = 32 rows each,
 // in registers.  Lane `part` of a column holds the rows ((i / 4) * SPLIT + part) * 4 + i % 4, so that the lanes of
-// a column read neighbouring 16-byte pieces of k, q and g from shared memory.  Tokens come in batches of 16 (8 for the
-// widest keys, whose batches would not fit the static shared memory otherwise).
+// a column read neighbouring 16-byte pieces of k, q and g from shared memory.  Tokens come in batches of BATCH
+// through two stages of shared memory: the next batch's k, q, g, v and beta are on their way (cp.async) while
+// this one is worked on.  A token's two sums over a lane's rows are kept in four partial sums each, added in a
+// fixed order.
 constexpr int kScanCols = 32;
+
+template <int DKP>
+struct ScanShared {
+    static constexpr int kBatch = DKP > 128 ? 8 : 16;
+    static constexpr int kStageFloats = kBatch * (3 * DKP + kScanCols + 1);   // k, q, g rows, v columns, beta
+    static constexpr size_t kBytes = 2 * kStageFloats * sizeof(float);
+};
+
+__device__ __forceinline__ void scan_copy_4(float* shared_destination, const float* global_source) {
+    const uint32_t destination = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(destination), "l"(global_source) : "memory");
+}
+__device__ __forceinline__ void scan_copy_16(float* shared_destination, const float* global_source) {
+    const uint32_t destination = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(destination), "l"(global_source) : "memory");
+}
 
 template <int DKP, int SPLIT>
 __global__ void __launch_bounds__(32 * SPLIT)
@@ -139,13 +157,10 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
                 const int* __restrict__ segment_length, const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv,
                 int num_slots, int* status) {
     constexpr int R = DKP / SPLIT;
-    constexpr int kScanBatch = DKP > 128 ? 8 : 16;
-    static_assert(R % 4 == 0, "rows per lane come in fours");
-    __shared__ __align__(16) float k_s[kScanBatch][DKP];
-    __shared__ __align__(16) float q_s[kScanBatch][DKP];
-    __shared__ __align__(16) float g_s[kScanBatch][DKP];
-    __shared__ float v_s[kScanBatch][kScanCols];
-    __shared__ float beta_s[kScanBatch];
+    using Shared = ScanShared<DKP>;
+    constexpr int kBatch = Shared::kBatch;
+    static_assert(R % 16 == 0, "rows per lane come in four partial sums of fours");
+    extern __shared__ __align__(16) float scan_memory[];
     const int segment = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kScanCols;
     const int tid = threadIdx.x, col = tid / SPLIT, part = tid % SPLIT;
     const int group = head / (heads / groups);
@@ -157,6 +172,54 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     const int start = segment_start[segment], length = segment_length[segment];
     const int column = col0 + col;
     const bool live = column < dv;
+    auto k_of = [&](int stage) { return scan_memory + stage * Shared::kStageFloats; };
+    auto q_of = [&](int stage) { return k_of(stage) + kBatch * DKP; };
+    auto g_of = [&](int stage) { return k_of(stage) + 2 * kBatch * DKP; };
+    auto v_of = [&](int stage) { return k_of(stage) + 3 * kBatch * DKP; };
+    auto beta_of = [&](int stage) { return v_of(stage) + kBatch * kScanCols; };
+    // The padding (rows of S past key_dim, columns past value_dim) is written once: the copies never touch it.
+    for (int index = tid; index < 2 * kBatch * DKP; index += blockDim.x) {
+        const int stage = index / (kBatch * DKP), rest = index - stage * kBatch * DKP;
+        if (rest % DKP >= dk) {
+            k_of(stage)[rest] = 0.0f;
+            q_of(stage)[rest] = 0.0f;
+            g_of(stage)[rest] = 1.0f;
+        }
+    }
+    for (int index = tid; index < 2 * kBatch * kScanCols; index += blockDim.x) {
+        const int stage = index / (kBatch * kScanCols), rest = index - stage * kBatch * kScanCols;
+        if (col0 + rest % kScanCols >= dv) v_of(stage)[rest] = 0.0f;
+    }
+    const bool wide = dk % 4 == 0;   // rows of 16-byte multiples (the buffers are 16-byte aligned)
+    auto fetch = [&](int stage, int t0) {
+        const int n = min(kBatch, length - t0);
+        if (wide) {
+            const int pieces = dk / 4;
+            for (int index = tid; index < n * pieces; index += blockDim.x) {
+                const int tt = index / pieces, c = 4 * (index - tt * pieces);
+                const size_t token = static_cast<size_t>(start + t0 + tt);
+                scan_copy_16(k_of(stage) + tt * DKP + c, k + (token * groups + group) * dk + c);
+                scan_copy_16(q_of(stage) + tt * DKP + c, q + (token * groups + group) * dk + c);
+                scan_copy_16(g_of(stage) + tt * DKP + c, g + (token * heads + head) * dk + c);
+            }
+        } else {
+            for (int index = tid; index < n * dk; index += blockDim.x) {
+                const int tt = index / dk, c = index - tt * dk;
+                const size_t token = static_cast<size_t>(start + t0 + tt);
+                scan_copy_4(k_of(stage) + tt * DKP + c, k + (token * groups + group) * dk + c);
+                scan_copy_4(q_of(stage) + tt * DKP + c, q + (token * groups + group) * dk + c);
+                scan_copy_4(g_of(stage) + tt * DKP + c, g + (token * heads + head) * dk + c);
+            }
+        }
+        const int columns = min(kScanCols, dv - col0);
+        for (int index = tid; index < n * columns; index += blockDim.x) {
+            const int tt = index / columns, c = index - tt * columns;
+            scan_copy_4(v_of(stage) + tt * kScanCols + c, v + (static_cast<size_t>(start + t0 + tt) * heads + head) * dv + col0 + c);
+        }
+        if (tid < n) scan_copy_4(beta_of(stage) + tid, beta + static_cast<size_t>(start + t0 + tid) * heads + head);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    fetch(0, 0);
     float* S_base = state + (static_cast<size_t>(slot) * heads + head) * dk * dv;
     float S[R];
 #pragma unroll
@@ -164,29 +227,23 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         const int row = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
         S[i] = (live && row < dk) ? S_base[static_cast<size_t>(row) * dv + column] : 0.0f;
     }
-    for (int t0 = 0; t0 < length; t0 += kScanBatch) {
-        const int n = min(kScanBatch, length - t0);
-        __syncthreads();   // the batch before is used up
-        for (int index = tid; index < n * DKP; index += blockDim.x) {
-            const int tt = index / DKP, c = index - tt * DKP;
-            const size_t token = static_cast<size_t>(start + t0 + tt);
-            const bool valid = c < dk;
-            k_s[tt][c] = valid ? k[(token * groups + group) * dk + c] : 0.0f;
-            q_s[tt][c] = valid ? q[(token * groups + group) * dk + c] : 0.0f;
-            g_s[tt][c] = valid ? g[(token * heads + head) * dk + c] : 1.0f;
+    int stage = 0;
+    for (int t0 = 0; t0 < length; t0 += kBatch, stage ^= 1) {
+        const int n = min(kBatch, length - t0);
+        if (t0 + kBatch < length) {
+            fetch(stage ^ 1, t0 + kBatch);   // that stage was used up in the turn before (the barrier at its end)
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
-        for (int index = tid; index < n * kScanCols; index += blockDim.x) {
-            const int tt = index / kScanCols, c = index - tt * kScanCols;
-            const size_t token = static_cast<size_t>(start + t0 + tt);
-            v_s[tt][c] = col0 + c < dv ? v[(token * heads + head) * dv + col0 + c] : 0.0f;
-        }
-        if (tid < n) beta_s[tid] = beta[static_cast<size_t>(start + t0 + tid) * heads + head];
         __syncthreads();
+        const float* v_s = v_of(stage);
+        const float* beta_s = beta_of(stage);
         for (int tt = 0; tt < n; ++tt) {
-            const float4* k4 = reinterpret_cast<const float4*>(k_s[tt]);
-            const float4* q4 = reinterpret_cast<const float4*>(q_s[tt]);
-            const float4* g4 = reinterpret_cast<const float4*>(g_s[tt]);
-            float dot = 0.0f;
+            const float4* k4 = reinterpret_cast<const float4*>(k_of(stage) + tt * DKP);
+            const float4* q4 = reinterpret_cast<const float4*>(q_of(stage) + tt * DKP);
+            const float4* g4 = reinterpret_cast<const float4*>(g_of(stage) + tt * DKP);
+            float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
                 const float4 decay = g4[(i >> 2) * SPLIT + part], key = k4[(i >> 2) * SPLIT + part];
@@ -194,15 +251,17 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
                 S[i + 1] *= decay.y;
                 S[i + 2] *= decay.z;
                 S[i + 3] *= decay.w;
+                float& dot = dots[(i >> 2) & 3];
                 dot += S[i] * key.x;
                 dot += S[i + 1] * key.y;
                 dot += S[i + 2] * key.z;
                 dot += S[i + 3] * key.w;
             }
+            float dot = (dots[0] + dots[1]) + (dots[2] + dots[3]);
 #pragma unroll
             for (int offset = 1; offset < SPLIT; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-            const float u = beta_s[tt] * (v_s[tt][col] - dot);
-            float o = 0.0f;
+            const float u = beta_s[tt] * (v_s[tt * kScanCols + col] - dot);
+            float reads[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
                 const float4 key = k4[(i >> 2) * SPLIT + part], query = q4[(i >> 2) * SPLIT + part];
@@ -210,15 +269,18 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
                 S[i + 1] += key.y * u;
                 S[i + 2] += key.z * u;
                 S[i + 3] += key.w * u;
-                o += S[i] * query.x;
-                o += S[i + 1] * query.y;
-                o += S[i + 2] * query.z;
-                o += S[i + 3] * query.w;
+                float& read = reads[(i >> 2) & 3];
+                read += S[i] * query.x;
+                read += S[i + 1] * query.y;
+                read += S[i + 2] * query.z;
+                read += S[i + 3] * query.w;
             }
+            float o = (reads[0] + reads[1]) + (reads[2] + reads[3]);
 #pragma unroll
             for (int offset = 1; offset < SPLIT; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
             if (part == 0 && live) out[(static_cast<size_t>(start + t0 + tt) * heads + head) * dv + column] = o;
         }
+        __syncthreads();   // this stage is refilled in the next turn
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -249,8 +311,10 @@ template <int DKP, int SPLIT>
 inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const float* k, const float* g, const float* v, const float* beta,
                         float* state, float* out, const int* segment_start, const int* segment_length, const int* segment_slot, int heads,
                         int groups, int dk, int dv, int num_slots, int* status) {
-    gdr_scan_kernel<DKP, SPLIT><<<grid, 32 * SPLIT, 0, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads,
-                                                                groups, dk, dv, num_slots, status);
+    static OncePerDevice once;
+    allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT>, static_cast<int>(ScanShared<DKP>::kBytes));
+    gdr_scan_kernel<DKP, SPLIT><<<grid, 32 * SPLIT, ScanShared<DKP>::kBytes, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot,
+                                                                                      heads, groups, dk, dv, num_slots, status);
 }
 
 }  // namespace lb
@@ -276,7 +340,7 @@ int lb_gdr_conv_state(const void* proj, int proj_width, void* conv_state, const 
                       const int* segment_slot, int segments, int channels, int taps, int num_slots, int dtype, cudaStream_t stream) {
     if (segments == 0 || taps <= 1) return 0;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::gdr_conv_state_kernel<T><<<segments, 256, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<T*>(conv_state), segment_start,
+        lb::gdr_conv_state_kernel<T><<<dim3(segments, (channels + 255) / 256), 256, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<T*>(conv_state), segment_start,
                                                                    segment_length, segment_slot, channels, taps, num_slots);
     })
     return LB_LAUNCH_RESULT();

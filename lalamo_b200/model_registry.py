@@ -102,9 +102,37 @@ def _lfm2_shape(hidden: int, heads: int, ff_dim: int) -> dict[str, Any]:
     }
 
 
-# Shapes of the published checkpoints, for the random-weights mode (no weights are downloaded).
+def _vuvulorn_shape(width: int, layers: int, left_heads: int, left_kv_heads: int, right_heads: int, right_dim: int, right_vdim: int, ff: int,
+                    experts: int, top: int, rank: int) -> dict[str, Any]:
+    """A Vuvulorn shape for the random-weights mode: head size 64 on the attention side under a window of 1,024 tokens
+    that keeps the first 4, dense and routed feed-forwards in turn, the routed ones with as many active columns
+    (``top`` experts of ``ff / top``) as the dense ones have."""
+    def mixer() -> dict[str, Any]:
+        return {
+            "left": {"heads": left_heads, "kv_heads": left_kv_heads, "dim": 64, "vdim": 64, "scale": 0.125,
+                     "mask": {"size": 1024, "keep_first": 4}, "rot": {"dims": 64, "base": 1000000.0}},
+            "right": {"heads": right_heads, "kv_heads": right_heads, "dim": right_dim, "vdim": right_vdim, "conv": 4, "decay_rank": rank, "gate_rank": rank},
+            "left_scale": 1.0,
+            "right_scale": 1.0,
+        }
+
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+    return {
+        "architecture": "Vuvulorn",
+        "vocab": 65536,
+        "width": width,
+        "norm": {"eps": 1e-6},
+        "layers": [{"type": "parallel", "mixer": mixer(), "mlp": routed if index % 2 else dense} for index in range(layers)],
+    }
+
+
+# Shapes of the published checkpoints, and Vuvulorn shapes of the same widths and depths, for the random-weights mode
+# (no weights are downloaded).
 PRESETS: dict[str, dict[str, Any]] = {
     "lfm2-350m": _lfm2_shape(1024, 16, 6656),
     "lfm2-700m": _lfm2_shape(1536, 24, 10240),
     "lfm2-1.2b": _lfm2_shape(2048, 32, 12288),
+    "vuvulorn-350m": _vuvulorn_shape(1024, 16, 16, 4, 8, 64, 128, 4608, 16, 4, 64),
+    "vuvulorn-1.2b": _vuvulorn_shape(2048, 16, 16, 4, 8, 128, 128, 8192, 16, 4, 64),
 }

@@ -816,11 +816,16 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: i
     return chosen, weights
 
 
+MOE_STREAM_MAX_PAIRS = 16  # up to this many (token, expert) pairs each pair streams its expert's weights; more are grouped by expert
+
+
 def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
-                activation: str = "silu") -> torch.Tensor:
+                activation: str = "silu", path: str | None = None) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * down[e] (act(gate[e] x[t]) * (up[e] x[t]))`` with ``e = chosen[t, k]``;
-    ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  Every (token, expert)
-    pair streams its expert's weights; the weighted sum is 32-bit, in the order of ``k``."""
+    ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  The weighted sum is
+    32-bit, in the order of ``k``; a pair whose expert is no expert counts nothing.  ``path`` forces one of the
+    three ways the pairs' products are computed (``"grouped"``, ``"stream"``, ``"plain"``); left out, the sizes
+    choose."""
     _check(x, "x")
     for name, tensor in (("gate", gate), ("up", up), ("down", down)):
         _check(tensor, name, x.dtype)
@@ -835,12 +840,40 @@ def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
         raise KernelError("moe_experts: shapes of x, the experts' weights, chosen and weights do not agree")
     if (width + ff) * 4 > 200 * 1024:
         raise KernelError("moe_experts: width + ff exceed the kernel's shared memory")
-    pair_out = torch.empty(tokens * top, width, dtype=torch.float32, device=x.device)
-    code = _lib().lb_moe_expert_stream(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(pair_out), c_int(tokens * top), c_int(top), c_int(width),
-                                       c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
-    _done(code, "moe_expert_stream")
+    pairs = tokens * top
+    pair_out = torch.empty(pairs, width, dtype=torch.float32, device=x.device)
+    vector = 8 if x.dtype == torch.bfloat16 else 4
+    wide_rows = width % vector == 0 and ff % vector == 0 and max(width, ff) * 4 <= 160 * 1024
+    lib = _lib()
+    if path is None:
+        path = "grouped" if x.dtype == torch.bfloat16 and wide_rows and experts <= 1024 and pairs > MOE_STREAM_MAX_PAIRS else "stream" if wide_rows else "plain"
+    if path == "grouped":
+        # many pairs: sorted by expert, 64 at a time on the tensor cores, every expert's weights read once per 64 pairs
+        if not (x.dtype == torch.bfloat16 and wide_rows and experts <= 1024):
+            raise KernelError("moe_experts: the grouped kernels take bfloat16, rows of 16-byte multiples and at most 1024 experts")
+        offsets = torch.empty(experts + 1, dtype=torch.int32, device=x.device)
+        order = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        hidden = torch.empty(pairs, ff, dtype=x.dtype, device=x.device)
+        code = lib.lb_moe_experts_grouped(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(offsets), _ptr(order), _ptr(hidden), _ptr(pair_out),
+                                          c_int(pairs), c_int(top), c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), _stream())
+        _done(code, "moe_experts_grouped", 3)
+    elif path == "stream":
+        # few pairs: each streams its expert's rows, 16 bytes a lane, the rows shared out over many blocks
+        if not wide_rows:
+            raise KernelError("moe_experts: the streaming kernels take rows of 16-byte multiples")
+        hidden = torch.empty(pairs, ff, dtype=x.dtype, device=x.device)
+        code = lib.lb_moe_expert_stream_wide(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(hidden), _ptr(pair_out), c_int(pairs), c_int(top),
+                                             c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
+        _done(code, "moe_expert_stream_wide", 2)
+    elif path == "plain":
+        code = lib.lb_moe_expert_stream(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(pair_out), c_int(pairs), c_int(top), c_int(width),
+                                        c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
+        _done(code, "moe_expert_stream")
+    else:
+        raise KernelError(f"moe_experts: unknown path {path!r}")
     out = torch.empty(tokens, width, dtype=x.dtype, device=x.device)
-    code = _lib().lb_moe_combine(_ptr(pair_out), _ptr(weights), _ptr(out), c_int(tokens), c_int(top), c_int(width), c_int(dtype_code(x.dtype)), _stream())
+    code = lib.lb_moe_combine(_ptr(pair_out), _ptr(weights), _ptr(chosen), c_int(experts), _ptr(out), c_int(tokens), c_int(top), c_int(width),
+                              c_int(dtype_code(x.dtype)), _stream())
     _done(code, "moe_combine")
     return out
 

@@ -385,18 +385,21 @@ def test_router_choice_and_weights(experts, top, count, keep):
     assert np.abs(weights.cpu().numpy() - want_weights).max() < 1e-5
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens", [1, 5, 150])
-def test_routed_experts(tokens, dtype):
+@pytest.mark.parametrize("path,dtype", [("plain", torch.float32), ("plain", torch.bfloat16), ("stream", torch.float32), ("stream", torch.bfloat16),
+                                        ("grouped", torch.bfloat16), (None, torch.bfloat16)])
+@pytest.mark.parametrize("tokens,width,ff,experts,top", [(1, 72, 40, 6, 3), (5, 72, 40, 6, 3), (150, 72, 40, 6, 3), (333, 256, 200, 9, 2), (70, 64, 328, 3, 3)])
+def test_routed_experts(tokens, width, ff, experts, top, path, dtype):
+    """Every way the experts' products are computed: a pair at a time (plain loads, 16-byte loads), and pairs grouped by
+    expert on the tensor cores (experts with no pair, with one, with more than a tile of 64)."""
     from lalamo_b200 import ops
 
     generator = np.random.default_rng(tokens)
-    width, ff, experts, top = 72, 40, 6, 3
     make = lambda *shape: torch.from_numpy(generator.standard_normal(shape)).to(dtype)
     x, gate, up, down = make(tokens, width), make(experts, ff, width) / 8, make(experts, ff, width) / 8, make(experts, width, ff) / 6
-    chosen = torch.from_numpy(np.stack([generator.permutation(experts)[:top] for _ in range(tokens)]).astype(np.int32))
+    usable = experts - 1 if experts > top else experts   # the last expert gets no pair at all where there are enough others
+    chosen = torch.from_numpy(np.stack([generator.permutation(usable)[:top] for _ in range(tokens)]).astype(np.int32))
     weights = torch.from_numpy(generator.random((tokens, top))).float()
-    got = ops.moe_experts(x.cuda(), gate.cuda(), up.cuda(), down.cuda(), chosen.cuda(), weights.cuda()).float().cpu().numpy()
+    got = ops.moe_experts(x.cuda(), gate.cuda(), up.cuda(), down.cuda(), chosen.cuda(), weights.cuda(), path=path).float().cpu().numpy()
     want = np.zeros((tokens, width))
     for t in range(tokens):
         for e, s in zip(chosen[t].tolist(), weights[t].double().numpy()):
