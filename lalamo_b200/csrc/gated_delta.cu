@@ -37,8 +37,8 @@ __device__ __forceinline__ float conv_silu(const T* __restrict__ proj, int proj_
     return acc * sigmoidf_(acc);
 }
 
-// One block per token, a warp per unit: the `groups` query heads, the `groups` key heads, the `heads` value
-// heads, and per head its decays and beta.
+// grid (tokens, slices of a token's units), a warp per unit: the `groups` query heads, the `groups` key heads, the
+// `heads` value heads, and per head its decays and beta.
 //   proj [tokens, proj_width]: q (groups x dk) | k (groups x dk) | v (heads x dv) | b (heads) | unused
 //   ag   [tokens, ag_width]:   a (heads x dk) | ...
 //   q_out, k_out [tokens, groups, dk], v_out [tokens, heads, dv], beta_out [tokens, heads], g_out [tokens, heads, dk]: 32-bit
@@ -64,7 +64,7 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
     const T* state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
     const int rel = token - start;
     const int units = 2 * groups + 2 * heads;
-    for (int unit = warp; unit < units; unit += warps) {
+    for (int unit = blockIdx.y * warps + warp; unit < units; unit += gridDim.y * warps) {
         if (unit < 2 * groups) {
             // a query or key head: convolution, silu, unit length (and the query's scale)
             const bool is_query = unit < groups;
@@ -125,19 +125,22 @@ __global__ void gdr_conv_state_kernel(const T* __restrict__ proj, int proj_width
     }
 }
 
-// The recurrence.  grid (portions, heads, ceil(dv / 32)); a block holds 32 columns of S, each column's DKP
-// (key_dim rounded up, padded rows stay zero) rows spread over SPLIT neighbouring lanes of R = 32 rows each,
-// in registers.  Lane `part` of a column holds the rows ((i / 4) * SPLIT + part) * 4 + i % 4, so that the lanes of
-// a column read neighbouring 16-byte pieces of k, q and g from shared memory.  Tokens come in batches of BATCH
-// through two stages of shared memory: the next batch's k, q, g, v and beta are on their way (cp.async) while
-// this one is worked on.  A token's two sums over a lane's rows are kept in four partial sums each, added in a
-// fixed order.
-constexpr int kScanCols = 32;
+// The recurrence.  grid (portions, heads, ceil(dv / 8)); a block holds 8 columns of S, a thread R = 8 rows of one
+// column in registers.  A column's DKP rows (key_dim rounded up, padded rows stay zero) are spread over SPLIT = DKP / 8
+// neighbouring lanes; lane `part` holds the rows ((i / 4) * SPLIT + part) * 4 + i % 4, so that the lanes of a column read
+// neighbouring 16-byte pieces of k, q and g from shared memory.  A token's step is one chain of dependent instructions
+// (decay, dot, the lanes' sums, write, read-out, the lanes' sums) that a warp issues in order, and a multiprocessor's
+// schedulers hold one warp each here, which issues about one instruction in three cycles: so the kernel is as fast as a
+// warp's instructions per token are few, hence many small blocks (a sequence of 2,048 tokens at 8 heads of 64 x 128
+// runs on 128 blocks of two warps).  Measured at those sizes: 32 rows x 1 column a lane 304 ns a token, 8 rows x 4
+// columns 382 ns, 8 rows x 1 column 273 ns.  Tokens come in batches through two stages of shared memory: the next
+// batch's k, q, g, v and beta are on their way (cp.async) while this one is worked on.  Every sum runs in a fixed order.
+constexpr int kScanCols = 8, kScanThreadCols = 1, kScanThreadRows = 8;
 
 template <int DKP>
 struct ScanShared {
     static constexpr int kBatch = DKP > 128 ? 8 : 16;
-    static constexpr int kStageFloats = kBatch * (3 * DKP + kScanCols + 1);   // k, q, g rows, v columns, beta
+    static constexpr int kStageFloats = kBatch * (3 * DKP + kScanCols + 4);   // k, q, g rows, v columns, beta (padded to 16 bytes)
     static constexpr size_t kBytes = 2 * kStageFloats * sizeof(float);
 };
 
@@ -151,18 +154,18 @@ __device__ __forceinline__ void scan_copy_16(float* shared_destination, const fl
 }
 
 template <int DKP, int SPLIT>
-__global__ void __launch_bounds__(32 * SPLIT)
+__global__ void __launch_bounds__((kScanCols / kScanThreadCols) * SPLIT)
 gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ g, const float* __restrict__ v,
                 const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ segment_start,
                 const int* __restrict__ segment_length, const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv,
                 int num_slots, int* status) {
-    constexpr int R = DKP / SPLIT;
+    constexpr int R = kScanThreadRows, C = kScanThreadCols;
+    static_assert(DKP == R * SPLIT && SPLIT <= 32, "a column's rows lie in one warp");
     using Shared = ScanShared<DKP>;
     constexpr int kBatch = Shared::kBatch;
-    static_assert(R % 16 == 0, "rows per lane come in four partial sums of fours");
     extern __shared__ __align__(16) float scan_memory[];
     const int segment = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kScanCols;
-    const int tid = threadIdx.x, col = tid / SPLIT, part = tid % SPLIT;
+    const int tid = threadIdx.x, column_group = tid / SPLIT, part = tid % SPLIT;
     const int group = head / (heads / groups);
     const int slot = segment_slot[segment];
     if (slot < 0 || slot >= num_slots) {
@@ -170,8 +173,7 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         return;
     }
     const int start = segment_start[segment], length = segment_length[segment];
-    const int column = col0 + col;
-    const bool live = column < dv;
+    const int column = col0 + C * column_group;   // the thread's first column
     auto k_of = [&](int stage) { return scan_memory + stage * Shared::kStageFloats; };
     auto q_of = [&](int stage) { return k_of(stage) + kBatch * DKP; };
     auto g_of = [&](int stage) { return k_of(stage) + 2 * kBatch * DKP; };
@@ -216,16 +218,17 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             const int tt = index / columns, c = index - tt * columns;
             scan_copy_4(v_of(stage) + tt * kScanCols + c, v + (static_cast<size_t>(start + t0 + tt) * heads + head) * dv + col0 + c);
         }
-        if (tid < n) scan_copy_4(beta_of(stage) + tid, beta + static_cast<size_t>(start + t0 + tid) * heads + head);
+        for (int tt = tid; tt < n; tt += blockDim.x) scan_copy_4(beta_of(stage) + tt, beta + static_cast<size_t>(start + t0 + tt) * heads + head);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
     fetch(0, 0);
     float* S_base = state + (static_cast<size_t>(slot) * heads + head) * dk * dv;
-    float S[R];
+    float S[C][R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int row = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
-        S[i] = (live && row < dk) ? S_base[static_cast<size_t>(row) * dv + column] : 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) S[c][i] = (row < dk && column + c < dv) ? S_base[static_cast<size_t>(row) * dv + column + c] : 0.0f;
     }
     int stage = 0;
     for (int t0 = 0; t0 < length; t0 += kBatch, stage ^= 1) {
@@ -237,65 +240,85 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
-        const float* v_s = v_of(stage);
         const float* beta_s = beta_of(stage);
         for (int tt = 0; tt < n; ++tt) {
             const float4* k4 = reinterpret_cast<const float4*>(k_of(stage) + tt * DKP);
             const float4* q4 = reinterpret_cast<const float4*>(q_of(stage) + tt * DKP);
             const float4* g4 = reinterpret_cast<const float4*>(g_of(stage) + tt * DKP);
-            float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float values[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) values[c] = v_of(stage)[tt * kScanCols + C * column_group + c];
+            float key[R], dots[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) dots[c] = 0.0f;
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
-                const float4 decay = g4[(i >> 2) * SPLIT + part], key = k4[(i >> 2) * SPLIT + part];
-                S[i] *= decay.x;
-                S[i + 1] *= decay.y;
-                S[i + 2] *= decay.z;
-                S[i + 3] *= decay.w;
-                float& dot = dots[(i >> 2) & 3];
-                dot += S[i] * key.x;
-                dot += S[i + 1] * key.y;
-                dot += S[i + 2] * key.z;
-                dot += S[i + 3] * key.w;
-            }
-            float dot = (dots[0] + dots[1]) + (dots[2] + dots[3]);
+                const float4 decay4 = g4[(i >> 2) * SPLIT + part], key4 = k4[(i >> 2) * SPLIT + part];
+                const float decay[4] = {decay4.x, decay4.y, decay4.z, decay4.w};
+                key[i] = key4.x, key[i + 1] = key4.y, key[i + 2] = key4.z, key[i + 3] = key4.w;
 #pragma unroll
-            for (int offset = 1; offset < SPLIT; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-            const float u = beta_s[tt] * (v_s[tt * kScanCols + col] - dot);
-            float reads[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        S[c][i + e] *= decay[e];
+                        dots[c] += S[c][i + e] * key[i + e];
+                    }
+                }
+            }
+#pragma unroll
+            for (int offset = 1; offset < SPLIT; offset <<= 1) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) dots[c] += __shfl_xor_sync(0xffffffffu, dots[c], offset);
+            }
+            float u[C], reads[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                u[c] = beta_s[tt] * (values[c] - dots[c]);
+                reads[c] = 0.0f;
+            }
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
-                const float4 key = k4[(i >> 2) * SPLIT + part], query = q4[(i >> 2) * SPLIT + part];
-                S[i] += key.x * u;
-                S[i + 1] += key.y * u;
-                S[i + 2] += key.z * u;
-                S[i + 3] += key.w * u;
-                float& read = reads[(i >> 2) & 3];
-                read += S[i] * query.x;
-                read += S[i + 1] * query.y;
-                read += S[i + 2] * query.z;
-                read += S[i + 3] * query.w;
-            }
-            float o = (reads[0] + reads[1]) + (reads[2] + reads[3]);
+                const float4 query4 = q4[(i >> 2) * SPLIT + part];
+                const float query[4] = {query4.x, query4.y, query4.z, query4.w};
 #pragma unroll
-            for (int offset = 1; offset < SPLIT; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-            if (part == 0 && live) out[(static_cast<size_t>(start + t0 + tt) * heads + head) * dv + column] = o;
+                for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        S[c][i + e] += key[i + e] * u[c];
+                        reads[c] += S[c][i + e] * query[e];
+                    }
+                }
+            }
+#pragma unroll
+            for (int offset = 1; offset < SPLIT; offset <<= 1) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) reads[c] += __shfl_xor_sync(0xffffffffu, reads[c], offset);
+            }
+            if (part == 0) {
+                float* destination = out + (static_cast<size_t>(start + t0 + tt) * heads + head) * dv + column;
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                    if (column + c < dv) destination[c] = reads[c];
+            }
         }
         __syncthreads();   // this stage is refilled in the next turn
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int row = ((i >> 2) * SPLIT + part) * 4 + (i & 3);
-        if (live && row < dk) S_base[static_cast<size_t>(row) * dv + column] = S[i];
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+            if (row < dk && column + c < dv) S_base[static_cast<size_t>(row) * dv + column + c] = S[c][i];
     }
 }
 
-// One block per token, a warp per head: out[t, h, :] = T(o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :])).
+// grid (tokens, slices of the heads), a warp per head: out[t, h, :] = T(o / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :])).
 template <typename T>
 __global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restrict__ ag, int ag_width, int gate_offset,
                                   const float* __restrict__ norm_weight, T* __restrict__ out, int heads, int dv, float eps) {
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int head = warp; head < heads; head += warps) {
+    for (int head = blockIdx.y * warps + warp; head < heads; head += gridDim.y * warps) {
         const float* row = o + (static_cast<size_t>(token) * heads + head) * dv;
         const T* gate = ag + static_cast<size_t>(token) * ag_width + gate_offset + static_cast<size_t>(head) * dv;
         float sum = 0.0f;
@@ -313,7 +336,7 @@ inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const fl
                         int groups, int dk, int dv, int num_slots, int* status) {
     static OncePerDevice once;
     allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT>, static_cast<int>(ScanShared<DKP>::kBytes));
-    gdr_scan_kernel<DKP, SPLIT><<<grid, 32 * SPLIT, ScanShared<DKP>::kBytes, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot,
+    gdr_scan_kernel<DKP, SPLIT><<<grid, (kScanCols / kScanThreadCols) * SPLIT, ScanShared<DKP>::kBytes, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot,
                                                                                       heads, groups, dk, dv, num_slots, status);
 }
 
@@ -328,7 +351,8 @@ int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_widt
     if (tokens == 0) return 0;
     if (dk > 32 * lb::kPrepareMaxPerLane || taps < 1 || heads % groups != 0) return -2;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::gdr_prepare_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
+        const int units = 2 * groups + 2 * heads;
+        lb::gdr_prepare_kernel<T><<<dim3(tokens, (units + 3) / 4), 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
                                                               static_cast<const T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
                                                               g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
                                                               unit_eps, q_scale, status);
@@ -353,13 +377,13 @@ int lb_gdr_scan(const float* q, const float* k, const float* g, const float* v, 
     if (dk < 1 || dk > 256 || dv < 1 || heads % groups != 0) return -2;
     const dim3 grid(segments, heads, (dv + lb::kScanCols - 1) / lb::kScanCols);
     if (dk <= 32)
-        lb::launch_scan<32, 1>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<32, 4>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
     else if (dk <= 64)
-        lb::launch_scan<64, 2>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<64, 8>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
     else if (dk <= 128)
-        lb::launch_scan<128, 4>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<128, 16>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
     else
-        lb::launch_scan<256, 8>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<256, 32>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
     return LB_LAUNCH_RESULT();
 }
 
@@ -367,7 +391,7 @@ int lb_gdr_output(const float* o, const void* ag, int ag_width, int gate_offset,
                   float eps, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::gdr_output_kernel<T><<<tokens, 128, 0, stream>>>(o, static_cast<const T*>(ag), ag_width, gate_offset, norm_weight, static_cast<T*>(out), heads, dv, eps);
+        lb::gdr_output_kernel<T><<<dim3(tokens, (heads + 3) / 4), 128, 0, stream>>>(o, static_cast<const T*>(ag), ag_width, gate_offset, norm_weight, static_cast<T*>(out), heads, dv, eps);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -196,6 +196,47 @@ def test_greedy_generation_through_the_entry_point(models, name):
     assert model.engine.cache.free_pages() == model.engine.cache.num_pages
 
 
+def test_command_line_and_step_replay(models, tmp_path):
+    """The same model through the two programs a user runs: `generate` (greedy ids of the plain implementation) and the
+    step replay that writes logits (portions, two live requests, a request that ends and another in its slot)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from trace_client import TraceRun
+
+    root = Path(__file__).resolve().parent.parent
+    folder, weights = models["Q"]
+    config = CONFIGS["Q"]
+    prompt = tokens_for(config, 11, 77)
+    prompt_file = tmp_path / "prompts.txt"
+    prompt_file.write_text(" ".join(str(token) for token in prompt) + "\n")
+    command = [sys.executable, "-m", "lalamo_b200", "generate", str(folder), "--prompt-ids-file", str(prompt_file), "--max-tokens", "5", "--temperature", "0",
+               "--dtype", "float32", "--max-cache-tokens", "256"]
+    result = subprocess.run(command, cwd=root, capture_output=True, text=True, timeout=600)
+    assert result.returncode == 0, result.stderr
+    produced = [json.loads(line) for line in result.stdout.splitlines() if line.startswith("{")][0]["token_ids"]
+    sequence = list(prompt)
+    for token in produced:
+        logits = plain.forward(config, weights, sequence)[-1]
+        best = np.sort(logits)[-2:]
+        if best[1] - best[0] < 1e-4:
+            break
+        assert token == int(np.argmax(logits))
+        sequence.append(token)
+
+    requests = {name: tokens_for(config, count, 80 + count) for name, count in (("a", 40), ("b", 9), ("c", 21))}
+    wanted = {name: plain.forward(config, weights, tokens) for name, tokens in requests.items()}
+    run = TraceRun(folder, "float32", tmp_path / "out", 128, config["vocab"])
+    steps = [([("a", 0, 17), ("b", 0, 2)], []), ([("a", 17, 18), ("b", 2, 9)], ["b"]), ([("a", 18, 40), ("c", 0, 21)], ["a", "c"])]
+    for entries, ended in steps:
+        got = run.step([{"id": name, "tokens": requests[name][lo:hi], "want": list(range(hi - lo))} for name, lo, hi in entries], ended)
+        want = np.concatenate([wanted[name][lo:hi] for name, lo, hi in entries])
+        assert row_errors(got, want).max() < FLOAT32_LIMIT
+    assert run.close() == 0
+
+
 # ---------------------------------------------------------------------- mechanisms alone
 def paged(keys: np.ndarray, values: np.ndarray, page_size: int, dtype: torch.dtype, seed: int):
     """Keys ``[n, groups, dim]`` and values ``[n, groups, vdim]`` of one request laid out in shuffled pages among NaN."""
