@@ -158,13 +158,16 @@ __global__ void __launch_bounds__((kScanCols / kScanThreadCols) * SPLIT)
 gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ g, const float* __restrict__ v,
                 const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ out, const int* __restrict__ segment_start,
                 const int* __restrict__ segment_length, const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv,
-                int num_slots, int* status) {
+                int num_slots, int* status, const int* __restrict__ segment_list, int v_columns) {
+    // segment_list (may be null): the portions this launch runs.  v_columns <= dv: the columns `v` really has (rows of
+    // heads x v_columns); the columns past them get zeros as values (they carry a transition matrix, see the chunked path).
     constexpr int R = kScanThreadRows, C = kScanThreadCols;
     static_assert(DKP == R * SPLIT && SPLIT <= 32, "a column's rows lie in one warp");
     using Shared = ScanShared<DKP>;
     constexpr int kBatch = Shared::kBatch;
     extern __shared__ __align__(16) float scan_memory[];
-    const int segment = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kScanCols;
+    const int segment = segment_list ? segment_list[blockIdx.x] : static_cast<int>(blockIdx.x);
+    const int head = blockIdx.y, col0 = blockIdx.z * kScanCols;
     const int tid = threadIdx.x, column_group = tid / SPLIT, part = tid % SPLIT;
     const int group = head / (heads / groups);
     const int slot = segment_slot[segment];
@@ -190,7 +193,7 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     }
     for (int index = tid; index < 2 * kBatch * kScanCols; index += blockDim.x) {
         const int stage = index / (kBatch * kScanCols), rest = index - stage * kBatch * kScanCols;
-        if (col0 + rest % kScanCols >= dv) v_of(stage)[rest] = 0.0f;
+        if (col0 + rest % kScanCols >= v_columns) v_of(stage)[rest] = 0.0f;
     }
     const bool wide = dk % 4 == 0;   // rows of 16-byte multiples (the buffers are 16-byte aligned)
     auto fetch = [&](int stage, int t0) {
@@ -213,10 +216,10 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
                 scan_copy_4(g_of(stage) + tt * DKP + c, g + (token * heads + head) * dk + c);
             }
         }
-        const int columns = min(kScanCols, dv - col0);
+        const int columns = min(kScanCols, v_columns - col0);
         for (int index = tid; index < n * columns; index += blockDim.x) {
             const int tt = index / columns, c = index - tt * columns;
-            scan_copy_4(v_of(stage) + tt * kScanCols + c, v + (static_cast<size_t>(start + t0 + tt) * heads + head) * dv + col0 + c);
+            scan_copy_4(v_of(stage) + tt * kScanCols + c, v + (static_cast<size_t>(start + t0 + tt) * heads + head) * v_columns + col0 + c);
         }
         for (int tt = tid; tt < n; tt += blockDim.x) scan_copy_4(beta_of(stage) + tt, beta + static_cast<size_t>(start + t0 + tt) * heads + head);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -330,14 +333,106 @@ __global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restri
     }
 }
 
+// ------------------------------------------------------------------------------------ long portions in chunks
+// The recurrence is linear in the state: S_t = M_t S_{t-1} + k_t (beta_t v_t)^T with M_t = (I - beta_t k_t k_t^T) diag(g_t).
+// A long portion is cut into chunks that the scan above runs side by side, each from a zero state and, in dk further
+// columns that start as the identity and take zeros as values, the chunk's transition P_t = M_t ... M_1; the scan's
+// read-out of those columns is P_t^T q_t.  With S_in the state at a chunk's start,
+//   S_t = S0_t + P_t S_in    and    o_t = o0_t + (P_t^T q_t)^T S_in,
+// so one short pass over a portion's chunks in order gives every chunk's S_in (and the portion's last state), and one
+// pass over the tokens adds the second term to the read-outs.  All in 32-bit.
+
+// state[chunk, head] (dk x (dv + dk)) = [0 | I].  One block per (chunk, head).
+__global__ void gdr_chunk_init_kernel(float* __restrict__ chunk_state, int dk, int dv) {
+    const int width = dv + dk;
+    float* S = chunk_state + static_cast<size_t>(blockIdx.x) * dk * width;
+    for (int index = threadIdx.x; index < dk * width; index += blockDim.x) {
+        const int row = index / width, col = index - row * width;
+        S[index] = col == dv + row ? 1.0f : 0.0f;
+    }
+}
+
+// grid (long portions, heads, ceil(dv / 32)), block (32, 32): thread (j, y) holds the rows y, y + 32, ... of column j of
+// S_in.  long_table rows: (portion, first chunk, chunks).  For each chunk in order: S_in is written to chunk_in[chunk]
+// (dk x dv per head), then S_in <- S0_L + P_L S_in.  The last S_in goes to the portion's state slot, from which the
+// first was read.
+constexpr int kPropagateRows = 8;   // dk <= 256
+__global__ void __launch_bounds__(1024)
+gdr_chunk_propagate_kernel(const float* __restrict__ chunk_state, float* __restrict__ chunk_in, float* __restrict__ state,
+                           const int* __restrict__ long_table, const int* __restrict__ segment_slot, int heads, int dk, int dv, int num_slots) {
+    extern __shared__ float s_in[];   // dk x 32
+    const int portion = long_table[3 * blockIdx.x], first_chunk = long_table[3 * blockIdx.x + 1], chunks = long_table[3 * blockIdx.x + 2];
+    const int head = blockIdx.y, j = threadIdx.x, column = blockIdx.z * 32 + j, y = threadIdx.y;
+    const int slot = segment_slot[portion];
+    if (slot < 0 || slot >= num_slots) return;   // reported by the kernels before
+    const bool live = column < dv;
+    const int width = dv + dk;
+    float* S_slot = state + (static_cast<size_t>(slot) * heads + head) * dk * dv;
+    float mine[kPropagateRows];
+#pragma unroll
+    for (int r = 0; r < kPropagateRows; ++r) {
+        const int row = y + 32 * r;
+        mine[r] = (live && row < dk) ? S_slot[static_cast<size_t>(row) * dv + column] : 0.0f;
+    }
+    for (int c = 0; c < chunks; ++c) {
+        const size_t chunk_head = static_cast<size_t>(first_chunk + c) * heads + head;
+        float* in_tile = chunk_in + chunk_head * dk * dv;
+        __syncthreads();   // the turn before has read s_in
+#pragma unroll
+        for (int r = 0; r < kPropagateRows; ++r) {
+            const int row = y + 32 * r;
+            if (row < dk) {
+                s_in[row * 32 + j] = mine[r];
+                if (live) in_tile[static_cast<size_t>(row) * dv + column] = mine[r];
+            }
+        }
+        __syncthreads();
+        const float* S_end = chunk_state + chunk_head * dk * width;   // [S0_L | P_L]
+#pragma unroll
+        for (int r = 0; r < kPropagateRows; ++r) {
+            const int row = y + 32 * r;
+            if (row < dk) {
+                const float* p_row = S_end + static_cast<size_t>(row) * width + dv;
+                float sum = live ? S_end[static_cast<size_t>(row) * width + column] : 0.0f;
+                for (int m = 0; m < dk; ++m) sum += p_row[m] * s_in[m * 32 + j];
+                mine[r] = sum;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kPropagateRows; ++r) {
+        const int row = y + 32 * r;
+        if (live && row < dk) S_slot[static_cast<size_t>(row) * dv + column] = mine[r];
+    }
+}
+
+// One block per (token of a chunk, head): out[t, h, j] = wide[t, h, j] + sum_m wide[t, h, dv + m] * chunk_in[chunk, h, m, j].
+// token_chunk[t] < 0: the token's portion ran unchunked, its read-out is in `out` already.
+__global__ void gdr_chunk_readout_kernel(const float* __restrict__ wide, const float* __restrict__ chunk_in, const int* __restrict__ token_chunk,
+                                         float* __restrict__ out, int heads, int dk, int dv) {
+    extern __shared__ float r_s[];   // dk
+    const int token = blockIdx.x, head = blockIdx.y;
+    const int chunk = token_chunk[token];
+    if (chunk < 0) return;
+    const float* row = wide + (static_cast<size_t>(token) * heads + head) * (dv + dk);
+    for (int m = threadIdx.x; m < dk; m += blockDim.x) r_s[m] = row[dv + m];
+    __syncthreads();
+    const float* S_in = chunk_in + (static_cast<size_t>(chunk) * heads + head) * dk * dv;
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+        float sum = row[j];
+        for (int m = 0; m < dk; ++m) sum += r_s[m] * S_in[static_cast<size_t>(m) * dv + j];
+        out[(static_cast<size_t>(token) * heads + head) * dv + j] = sum;
+    }
+}
+
 template <int DKP, int SPLIT>
 inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const float* k, const float* g, const float* v, const float* beta,
                         float* state, float* out, const int* segment_start, const int* segment_length, const int* segment_slot, int heads,
-                        int groups, int dk, int dv, int num_slots, int* status) {
+                        int groups, int dk, int dv, int num_slots, int* status, const int* segment_list, int v_columns) {
     static OncePerDevice once;
     allow_shared_memory(once, gdr_scan_kernel<DKP, SPLIT>, static_cast<int>(ScanShared<DKP>::kBytes));
     gdr_scan_kernel<DKP, SPLIT><<<grid, (kScanCols / kScanThreadCols) * SPLIT, ScanShared<DKP>::kBytes, stream>>>(q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot,
-                                                                                      heads, groups, dk, dv, num_slots, status);
+                                                                                      heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
 }
 
 }  // namespace lb
@@ -370,20 +465,42 @@ int lb_gdr_conv_state(const void* proj, int proj_width, void* conv_state, const 
     return LB_LAUNCH_RESULT();
 }
 
+// segment_list (may be null): the portions to run, `segments` of them.  v_columns: the columns `v` has (0: dv).
 int lb_gdr_scan(const float* q, const float* k, const float* g, const float* v, const float* beta, float* state, float* out,
                 const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int heads, int groups, int dk, int dv,
-                int num_slots, int* status, cudaStream_t stream) {
+                int num_slots, int* status, cudaStream_t stream, const int* segment_list, int v_columns) {
     if (segments == 0) return 0;
-    if (dk < 1 || dk > 256 || dv < 1 || heads % groups != 0) return -2;
+    if (v_columns <= 0) v_columns = dv;
+    if (dk < 1 || dk > 256 || dv < 1 || heads % groups != 0 || v_columns > dv) return -2;
     const dim3 grid(segments, heads, (dv + lb::kScanCols - 1) / lb::kScanCols);
     if (dk <= 32)
-        lb::launch_scan<32, 4>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<32, 4>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
     else if (dk <= 64)
-        lb::launch_scan<64, 8>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<64, 8>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
     else if (dk <= 128)
-        lb::launch_scan<128, 16>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<128, 16>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
     else
-        lb::launch_scan<256, 32>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status);
+        lb::launch_scan<256, 32>(grid, stream, q, k, g, v, beta, state, out, segment_start, segment_length, segment_slot, heads, groups, dk, dv, num_slots, status, segment_list, v_columns);
+    return LB_LAUNCH_RESULT();
+}
+
+// The passes around the chunks' scan (which is lb_gdr_scan over the chunk tables with dv + dk columns): `chunk_state`
+// [chunks, heads, dk, dv + dk] is set to [0 | I] by lb_gdr_chunk_init before the scan; after it lb_gdr_chunk_finish gives every
+// chunk its incoming state (`chunk_in` [chunks, heads, dk, dv]), the portions' slots their last state, and the tokens
+// of chunks their read-out (`wide` [tokens, heads, dv + dk] is what the scan wrote; `out` [tokens, heads, dv]).
+int lb_gdr_chunk_init(float* chunk_state, int chunks, int heads, int dk, int dv, cudaStream_t stream) {
+    if (chunks == 0) return 0;
+    lb::gdr_chunk_init_kernel<<<chunks * heads, 256, 0, stream>>>(chunk_state, dk, dv);
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_gdr_chunk_finish(const float* chunk_state, float* chunk_in, float* state, const float* wide, float* out, const int* long_table, int long_portions,
+                        const int* segment_slot, const int* token_chunk, int tokens, int heads, int dk, int dv, int num_slots, cudaStream_t stream) {
+    if (long_portions == 0) return 0;
+    if (dk > 32 * lb::kPropagateRows) return -2;
+    lb::gdr_chunk_propagate_kernel<<<dim3(long_portions, heads, (dv + 31) / 32), dim3(32, 32), static_cast<size_t>(dk) * 32 * sizeof(float), stream>>>(
+        chunk_state, chunk_in, state, long_table, segment_slot, heads, dk, dv, num_slots);
+    lb::gdr_chunk_readout_kernel<<<dim3(tokens, heads), 128, static_cast<size_t>(dk) * sizeof(float), stream>>>(wide, chunk_in, token_chunk, out, heads, dk, dv);
     return LB_LAUNCH_RESULT();
 }
 

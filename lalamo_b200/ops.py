@@ -698,6 +698,35 @@ def short_conv(
 
 
 # ---------------------------------------------------------------------- gated delta rule
+GDR_CHUNK_TOKENS = 128  # long portions are scanned in chunks of this many tokens, side by side
+GDR_LONG_PORTION = 384  # portions of at least this many tokens count as long
+
+
+def gated_delta_chunk_plan(starts, lengths, chunk_tokens: int = GDR_CHUNK_TOKENS, long_portion: int = GDR_LONG_PORTION) -> dict:
+    """The host's part of the chunked gated delta rule, from the portions' first rows and lengths alone: ``direct``
+    (the portions scanned whole), ``chunk_start`` / ``chunk_length`` / ``chunk_slot`` (the chunks of the long portions,
+    each with a temporary state of its own), ``long_table`` (per long portion: its index, its first chunk, its number of
+    chunks) and ``token_chunk`` (per row of the step its chunk, or -1).  NumPy int32 arrays."""
+    import numpy as np
+
+    direct, chunk_start, chunk_length, long_table = [], [], [], []
+    token_chunk = np.full(int(sum(lengths)), -1, dtype=np.int32)
+    for index, (start, length) in enumerate(zip(starts, lengths)):
+        if length < long_portion:
+            direct.append(index)
+            continue
+        first = len(chunk_start)
+        for offset in range(0, length, chunk_tokens):
+            count = min(chunk_tokens, length - offset)
+            token_chunk[start + offset : start + offset + count] = len(chunk_start)
+            chunk_start.append(start + offset)
+            chunk_length.append(count)
+        long_table.append((index, first, len(chunk_start) - first))
+    as_array = lambda values: np.asarray(values, dtype=np.int32).reshape(-1)
+    return {"direct": as_array(direct), "chunk_start": as_array(chunk_start), "chunk_length": as_array(chunk_length),
+            "chunk_slot": np.arange(len(chunk_start), dtype=np.int32), "long_table": as_array(long_table), "token_chunk": token_chunk}
+
+
 def gated_delta_rule(
     proj: torch.Tensor,
     low_rank: torch.Tensor,
@@ -720,9 +749,12 @@ def gated_delta_rule(
     segment_slot: torch.Tensor,
     segments: int,
     status: torch.Tensor,
+    chunk_plan: dict | None = None,
 ) -> torch.Tensor:
     """The gated delta rule with a decay per head and key channel over the step's portions, from each
-    request's state slot and back into it.
+    request's state slot and back into it.  ``chunk_plan`` (see :func:`gated_delta_chunk_plan`; int32 arrays on
+    the device with their sizes) lets long portions run as chunks side by side; without it every portion is
+    scanned from its first token to its last.
 
     ``proj`` ``[tokens, >= C + heads]`` holds, per token, the pre-convolution q (``groups x key_dim``), k
     (the same) and v (``heads x value_dim``), ``C`` channels in all, then one beta logit per head;
@@ -773,10 +805,30 @@ def gated_delta_rule(
                                      c_int(segments), c_int(channels), c_int(taps), c_int(num_slots), c_int(dtype_code(proj.dtype)), _stream())
         _done(code, "gdr_conv_state")
     read_out = torch.empty(tokens, num_heads, value_dim, dtype=torch.float32, device=device)
-    code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(beta), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
-                           _ptr(segment_slot), c_int(segments), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(num_slots),
-                           _ptr(status), _stream())
-    _done(code, "gdr_scan")
+    direct_list, num_direct = None, segments
+    if chunk_plan is not None and chunk_plan["num_chunks"] > 0:
+        # Long portions: their chunks are scanned side by side from zero states, with key_dim further columns that carry
+        # each chunk's transition; then the chunks' incoming states in order, and the read-outs' second term.
+        num_chunks, num_long = chunk_plan["num_chunks"], chunk_plan["num_long"]
+        wide_dim = value_dim + key_dim
+        wide = torch.empty(tokens, num_heads, wide_dim, dtype=torch.float32, device=device)
+        chunk_state = torch.empty(num_chunks, num_heads, key_dim, wide_dim, dtype=torch.float32, device=device)
+        chunk_in = torch.empty(num_chunks, num_heads, key_dim, value_dim, dtype=torch.float32, device=device)
+        _done(lib.lb_gdr_chunk_init(_ptr(chunk_state), c_int(num_chunks), c_int(num_heads), c_int(key_dim), c_int(value_dim), _stream()), "gdr_chunk_init")
+        code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(beta), _ptr(chunk_state), _ptr(wide), _ptr(chunk_plan["chunk_start"]),
+                               _ptr(chunk_plan["chunk_length"]), _ptr(chunk_plan["chunk_slot"]), c_int(num_chunks), c_int(num_heads), c_int(num_groups),
+                               c_int(key_dim), c_int(wide_dim), c_int(num_chunks), _ptr(status), _stream(), _ptr(None), c_int(value_dim))
+        _done(code, "gdr_scan (chunks)")
+        code = lib.lb_gdr_chunk_finish(_ptr(chunk_state), _ptr(chunk_in), _ptr(matrix_state), _ptr(wide), _ptr(read_out), _ptr(chunk_plan["long_table"]),
+                                       c_int(num_long), _ptr(segment_slot), _ptr(chunk_plan["token_chunk"]), c_int(tokens), c_int(num_heads), c_int(key_dim),
+                                       c_int(value_dim), c_int(num_slots), _stream())
+        _done(code, "gdr_chunk_finish", 2)
+        direct_list, num_direct = chunk_plan["direct"], chunk_plan["num_direct"]
+    if num_direct > 0:
+        code = lib.lb_gdr_scan(_ptr(q), _ptr(k), _ptr(decay), _ptr(v), _ptr(beta), _ptr(matrix_state), _ptr(read_out), _ptr(segment_start), _ptr(segment_length),
+                               _ptr(segment_slot), c_int(num_direct), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(num_slots),
+                               _ptr(status), _stream(), _ptr(direct_list), c_int(value_dim))
+        _done(code, "gdr_scan")
     out = torch.empty(tokens, num_heads * value_dim, dtype=proj.dtype, device=device)
     code = lib.lb_gdr_output(_ptr(read_out), _ptr(low_rank), c_int(low_rank.shape[1]), c_int(num_heads * key_dim), _ptr(norm_weight), _ptr(out), c_int(tokens),
                              c_int(num_heads), c_int(value_dim), c_float(norm_eps), c_int(dtype_code(proj.dtype)), _stream())

@@ -12,11 +12,12 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.plan import GatedDeltaSpec
-from .base import CacheNeed, CompositeNeed, CompositeView, Mixer, Runtime, SlotStateNeed, StepInputs, TensorDecl, register_part
+from .base import CacheNeed, CompositeNeed, CompositeView, HostSegments, Mixer, Runtime, SlotStateNeed, StepInputs, TensorDecl, register_part
 
 __all__ = ["GatedDelta"]
 
@@ -83,12 +84,24 @@ class GatedDelta(Mixer):
         conv = SlotStateNeed(shape=(max(spec.conv_taps - 1, 1), self.channels))
         return CompositeNeed((matrix, conv))
 
+    # Long portions run in chunks side by side; which rows belong to which chunk depends on the portions' lengths
+    # only, and is the same for every layer of this kind.
+    step_plan_uses_context = False
+
+    def step_plan_key(self) -> object:
+        return ("gated_delta", ops.GDR_CHUNK_TOKENS, ops.GDR_LONG_PORTION)
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
+        return ops.gated_delta_chunk_plan(segments.start, segments.length)
+
     def forward(self, x: torch.Tensor, step: StepInputs, cache: CompositeView) -> torch.Tensor:  # type: ignore[override]
         spec = self.spec
         matrix_view, conv_view = cache.views
         if not cache.owns:
             raise ValueError("a gated-delta layer cannot read another layer's state")
         status = self.runtime.status
+        lists, host_lists = step.plan_of(self)
+        chunk_plan = dict(lists, num_chunks=host_lists["chunk_start"].size, num_long=host_lists["long_table"].size // 3, num_direct=host_lists["direct"].size)
         proj = ops.linear(x, self.in_proj, status=status)
         low = ops.linear(x, self.low_rank_down, status=status)
         logits = ops.linear(low, self.low_rank_up, status=status)
@@ -113,5 +126,6 @@ class GatedDelta(Mixer):
             segment_slot=matrix_view.segment_slot,
             segments=step.segments,
             status=status,
+            chunk_plan=chunk_plan,
         )
         return ops.linear(read_out, self.out_proj, status=status)

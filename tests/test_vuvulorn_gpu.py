@@ -145,6 +145,20 @@ def test_mixed_batches_with_pages_and_slots_used_again(models, name, dtype):
     assert engine.cache.free_pages() == engine.cache.num_pages
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["P", "R"])
+def test_long_portions(models, name, dtype):
+    """Portions long enough for the recurrence to run them as chunks side by side, beside a short request, then decoding."""
+    folder, weights = models[name]
+    config = CONFIGS[name]
+    requests = {"a": tokens_for(config, 1100, 41), "b": tokens_for(config, 30, 42)}
+    schedule = [[("a", 600), ("b", 5)], [("a", 1), ("b", 20)], [("a", 490), ("b", 1)], [("b", 4), ("a", 9)]]
+    engine = load_engine(folder, dtype, max_tokens=2048)
+    got = run_schedule(engine, requests, schedule)
+    for key, tokens in requests.items():
+        assert close_enough(got[key], plain.forward(config, weights, tokens), dtype), key
+
+
 def test_a_window_gives_pages_back_and_keeps_the_first_ones(models):
     """A request four times as long as the pool runs in portions, since its windows free the pages they have passed;
     the pages of the kept first tokens stay, and decoding goes on over them."""
@@ -347,15 +361,21 @@ def test_tensor_core_attention_with_kept_first_keys(window, keep_first, special,
     assert worst.max() < 0.5, (int(worst.argmax()), float(worst.max()))
 
 
+LONG_STEPS = [{0: 3, 1: 1}, {0: 500, 1: 20}, {0: 1, 1: 2}, {1: 14, 0: 385}, {0: 11}]   # portions long enough to run as chunks, a last chunk of one token
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,groups,dk,dv,taps", [(2, 1, 16, 32, 3), (3, 3, 40, 24, 1), (2, 2, 72, 16, 4), (4, 2, 128, 64, 2), (1, 1, 160, 40, 3)])
-def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, dv, taps, dtype):
-    """Two requests in different slots, cut differently, a far write that must survive hundreds of decays close to one."""
+@pytest.mark.parametrize("heads,groups,dk,dv,taps,steps", [
+    (2, 1, 16, 32, 3, None), (3, 3, 40, 24, 1, None), (2, 2, 72, 16, 4, None), (4, 2, 128, 64, 2, None), (1, 1, 160, 40, 3, None),
+    (2, 1, 16, 32, 3, LONG_STEPS), (2, 2, 64, 128, 4, LONG_STEPS), (3, 1, 40, 20, 2, LONG_STEPS), (1, 1, 128, 72, 3, LONG_STEPS)])
+def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, dv, taps, steps, dtype):
+    """Two requests in different slots, cut differently, a far write that must survive hundreds of decays close to one;
+    with long portions, which run as chunks side by side from zero states and are put together afterwards."""
     from lalamo_b200 import ops
 
     generator = np.random.default_rng(dk * dv + taps)
     channels = 2 * groups * dk + heads * dv
-    lengths = {0: 150, 1: 37}
+    lengths = {0: 150, 1: 37} if steps is None else {0: 900, 1: 37}
     proj = {r: torch.from_numpy(generator.standard_normal((n, channels + heads))).to(dtype) for r, n in lengths.items()}
     low = {r: torch.from_numpy(generator.standard_normal((n, heads * (dk + dv)))).to(dtype) for r, n in lengths.items()}
     conv = torch.from_numpy(0.6 * generator.standard_normal((channels, taps))).float()
@@ -387,7 +407,7 @@ def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, 
         matrix_state[slot] = 0
         conv_state[slot] = 0
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    steps = [{0: 3, 1: 1}, {0: 1, 1: 20}, {0: 64}, {1: 2, 0: 2}, {0: 17, 1: 14}, {0: 63}]
+    steps = steps or [{0: 3, 1: 1}, {0: 1, 1: 20}, {0: 64}, {1: 2, 0: 2}, {0: 17, 1: 14}, {0: 63}]
     done = {0: 0, 1: 0}
     got = {0: [], 1: []}
     for step in steps:
@@ -397,10 +417,14 @@ def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, 
         counts = [step[r] for r in order]
         starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
         as_int = lambda values: torch.tensor(list(values), dtype=torch.int32, device="cuda")
+        plan = ops.gated_delta_chunk_plan(starts.tolist(), counts)
+        chunk_plan = {name: as_int(array.tolist()) for name, array in plan.items()}
+        chunk_plan.update(num_chunks=plan["chunk_start"].size, num_long=plan["long_table"].size // 3, num_direct=plan["direct"].size)
         out = ops.gated_delta_rule(
             rows, lows, conv_state if taps > 1 else None, matrix_state, conv_weight=conv.cuda(), a_log=a_log.cuda(), dt_bias=dt_bias.cuda(), norm_weight=norm.cuda(),
             norm_eps=eps, num_heads=heads, num_groups=groups, key_dim=dk, value_dim=dv, unit_eps=1e-6, token_segment=as_int(np.repeat(np.arange(len(order)), counts)),
-            segment_start=as_int(starts), segment_length=as_int(counts), segment_slot=as_int(slot_of[r] for r in order), segments=len(order), status=status)
+            segment_start=as_int(starts), segment_length=as_int(counts), segment_slot=as_int(slot_of[r] for r in order), segments=len(order), status=status,
+            chunk_plan=chunk_plan)
         out = out.float().cpu().numpy()
         for r, start, count in zip(order, starts, counts):
             got[r].append(out[start : start + count])
