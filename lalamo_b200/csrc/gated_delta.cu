@@ -139,7 +139,7 @@ constexpr int kScanCols = 8, kScanThreadCols = 1, kScanThreadRows = 8;
 
 template <int DKP>
 struct ScanShared {
-    static constexpr int kBatch = DKP > 128 ? 8 : 16;
+    static constexpr int kBatch = 8;   // small stages: many blocks fit a multiprocessor, whose warps hide each other's waits
     static constexpr int kStageFloats = kBatch * (3 * DKP + kScanCols + 4);   // k, q, g rows, v columns, beta (padded to 16 bytes)
     static constexpr size_t kBytes = 2 * kStageFloats * sizeof(float);
 };
@@ -354,19 +354,22 @@ __global__ void gdr_chunk_init_kernel(float* __restrict__ chunk_state, int dk, i
 
 // grid (long portions, heads, ceil(dv / 32)), block (32, 32): thread (j, y) holds the rows y, y + 32, ... of column j of
 // S_in.  long_table rows: (portion, first chunk, chunks).  For each chunk in order: S_in is written to chunk_in[chunk]
-// (dk x dv per head), then S_in <- S0_L + P_L S_in.  The last S_in goes to the portion's state slot, from which the
-// first was read.
+// (dk x dv per head), then S_in <- S0_L + P_L S_in, with P_L staged in shared memory where it fits (p_in_shared).  The
+// last S_in goes to the portion's state slot, from which the first was read.
 constexpr int kPropagateRows = 8;   // dk <= 256
 __global__ void __launch_bounds__(1024)
 gdr_chunk_propagate_kernel(const float* __restrict__ chunk_state, float* __restrict__ chunk_in, float* __restrict__ state,
-                           const int* __restrict__ long_table, const int* __restrict__ segment_slot, int heads, int dk, int dv, int num_slots) {
-    extern __shared__ float s_in[];   // dk x 32
+                           const int* __restrict__ long_table, const int* __restrict__ segment_slot, int heads, int dk, int dv, int num_slots,
+                           int p_in_shared) {
+    extern __shared__ float propagate_memory[];
+    float* s_in = propagate_memory;          // dk x 32
+    float* p_s = propagate_memory + dk * 32;   // dk x (dk + 1) if p_in_shared
     const int portion = long_table[3 * blockIdx.x], first_chunk = long_table[3 * blockIdx.x + 1], chunks = long_table[3 * blockIdx.x + 2];
     const int head = blockIdx.y, j = threadIdx.x, column = blockIdx.z * 32 + j, y = threadIdx.y;
     const int slot = segment_slot[portion];
     if (slot < 0 || slot >= num_slots) return;   // reported by the kernels before
     const bool live = column < dv;
-    const int width = dv + dk;
+    const int width = dv + dk, pitch = dk + 1;
     float* S_slot = state + (static_cast<size_t>(slot) * heads + head) * dk * dv;
     float mine[kPropagateRows];
 #pragma unroll
@@ -377,7 +380,8 @@ gdr_chunk_propagate_kernel(const float* __restrict__ chunk_state, float* __restr
     for (int c = 0; c < chunks; ++c) {
         const size_t chunk_head = static_cast<size_t>(first_chunk + c) * heads + head;
         float* in_tile = chunk_in + chunk_head * dk * dv;
-        __syncthreads();   // the turn before has read s_in
+        const float* S_end = chunk_state + chunk_head * dk * width;   // [S0_L | P_L]
+        __syncthreads();   // the turn before has read s_in and p_s
 #pragma unroll
         for (int r = 0; r < kPropagateRows; ++r) {
             const int row = y + 32 * r;
@@ -386,16 +390,26 @@ gdr_chunk_propagate_kernel(const float* __restrict__ chunk_state, float* __restr
                 if (live) in_tile[static_cast<size_t>(row) * dv + column] = mine[r];
             }
         }
+        if (p_in_shared) {
+            for (int index = y * 32 + j; index < dk * dk; index += 1024) {
+                const int row = index / dk, m = index - row * dk;
+                p_s[row * pitch + m] = S_end[static_cast<size_t>(row) * width + dv + m];
+            }
+        }
         __syncthreads();
-        const float* S_end = chunk_state + chunk_head * dk * width;   // [S0_L | P_L]
 #pragma unroll
         for (int r = 0; r < kPropagateRows; ++r) {
             const int row = y + 32 * r;
             if (row < dk) {
-                const float* p_row = S_end + static_cast<size_t>(row) * width + dv;
-                float sum = live ? S_end[static_cast<size_t>(row) * width + column] : 0.0f;
-                for (int m = 0; m < dk; ++m) sum += p_row[m] * s_in[m * 32 + j];
-                mine[r] = sum;
+                const float* p_row = p_in_shared ? p_s + row * pitch : S_end + static_cast<size_t>(row) * width + dv;
+                float sums[4] = {live ? S_end[static_cast<size_t>(row) * width + column] : 0.0f, 0.0f, 0.0f, 0.0f};
+                int m = 0;
+                for (; m + 4 <= dk; m += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sums[e] += p_row[m + e] * s_in[(m + e) * 32 + j];
+                }
+                for (; m < dk; ++m) sums[0] += p_row[m] * s_in[m * 32 + j];
+                mine[r] = (sums[0] + sums[1]) + (sums[2] + sums[3]);
             }
         }
     }
@@ -406,22 +420,35 @@ gdr_chunk_propagate_kernel(const float* __restrict__ chunk_state, float* __restr
     }
 }
 
-// One block per (token of a chunk, head): out[t, h, j] = wide[t, h, j] + sum_m wide[t, h, dv + m] * chunk_in[chunk, h, m, j].
-// token_chunk[t] < 0: the token's portion ran unchunked, its read-out is in `out` already.
-__global__ void gdr_chunk_readout_kernel(const float* __restrict__ wide, const float* __restrict__ chunk_in, const int* __restrict__ token_chunk,
-                                         float* __restrict__ out, int heads, int dk, int dv) {
-    extern __shared__ float r_s[];   // dk
-    const int token = blockIdx.x, head = blockIdx.y;
-    const int chunk = token_chunk[token];
-    if (chunk < 0) return;
-    const float* row = wide + (static_cast<size_t>(token) * heads + head) * (dv + dk);
-    for (int m = threadIdx.x; m < dk; m += blockDim.x) r_s[m] = row[dv + m];
+// grid (chunks x tiles of 16 tokens, heads): out[t, h, j] = wide[t, h, j] + sum_m wide[t, h, dv + m] * chunk_in[chunk, h, m, j]
+// for the tile's tokens, which share what is read of chunk_in.
+constexpr int kReadoutTokens = 16;
+__global__ void gdr_chunk_readout_kernel(const float* __restrict__ wide, const float* __restrict__ chunk_in, const int* __restrict__ chunk_start,
+                                         const int* __restrict__ chunk_length, int tiles_per_chunk, float* __restrict__ out, int heads, int dk, int dv) {
+    extern __shared__ float r_s[];   // 16 x dk
+    const int chunk = blockIdx.x / tiles_per_chunk, tile = blockIdx.x - chunk * tiles_per_chunk, head = blockIdx.y;
+    const int first = kReadoutTokens * tile, count = min(kReadoutTokens, chunk_length[chunk] - first);
+    if (count <= 0) return;
+    const int token0 = chunk_start[chunk] + first;
+    for (int index = threadIdx.x; index < count * dk; index += blockDim.x) {
+        const int tt = index / dk, m = index - tt * dk;
+        r_s[tt * dk + m] = wide[(static_cast<size_t>(token0 + tt) * heads + head) * (dv + dk) + dv + m];
+    }
     __syncthreads();
     const float* S_in = chunk_in + (static_cast<size_t>(chunk) * heads + head) * dk * dv;
     for (int j = threadIdx.x; j < dv; j += blockDim.x) {
-        float sum = row[j];
-        for (int m = 0; m < dk; ++m) sum += r_s[m] * S_in[static_cast<size_t>(m) * dv + j];
-        out[(static_cast<size_t>(token) * heads + head) * dv + j] = sum;
+        float sums[kReadoutTokens];
+#pragma unroll
+        for (int tt = 0; tt < kReadoutTokens; ++tt) sums[tt] = tt < count ? wide[(static_cast<size_t>(token0 + tt) * heads + head) * (dv + dk) + j] : 0.0f;
+#pragma unroll 4
+        for (int m = 0; m < dk; ++m) {   // four loads of S_in on their way at a time
+            const float s = S_in[static_cast<size_t>(m) * dv + j];
+#pragma unroll
+            for (int tt = 0; tt < kReadoutTokens; ++tt) sums[tt] += r_s[(tt < count ? tt : 0) * dk + m] * s;
+        }
+#pragma unroll
+        for (int tt = 0; tt < kReadoutTokens; ++tt)
+            if (tt < count) out[(static_cast<size_t>(token0 + tt) * heads + head) * dv + j] = sums[tt];
     }
 }
 
@@ -495,12 +522,21 @@ int lb_gdr_chunk_init(float* chunk_state, int chunks, int heads, int dk, int dv,
 }
 
 int lb_gdr_chunk_finish(const float* chunk_state, float* chunk_in, float* state, const float* wide, float* out, const int* long_table, int long_portions,
-                        const int* segment_slot, const int* token_chunk, int tokens, int heads, int dk, int dv, int num_slots, cudaStream_t stream) {
-    if (long_portions == 0) return 0;
-    if (dk > 32 * lb::kPropagateRows) return -2;
-    lb::gdr_chunk_propagate_kernel<<<dim3(long_portions, heads, (dv + 31) / 32), dim3(32, 32), static_cast<size_t>(dk) * 32 * sizeof(float), stream>>>(
-        chunk_state, chunk_in, state, long_table, segment_slot, heads, dk, dv, num_slots);
-    lb::gdr_chunk_readout_kernel<<<dim3(tokens, heads), 128, static_cast<size_t>(dk) * sizeof(float), stream>>>(wide, chunk_in, token_chunk, out, heads, dk, dv);
+                        const int* segment_slot, const int* chunk_start, const int* chunk_length, int chunks, int chunk_tokens, int heads, int dk, int dv,
+                        int num_slots, cudaStream_t stream) {
+    if (long_portions == 0 || chunks == 0) return 0;
+    if (dk > 32 * lb::kPropagateRows || chunk_tokens < 1) return -2;
+    size_t shared = static_cast<size_t>(dk) * 32 * sizeof(float);
+    const size_t with_p = shared + static_cast<size_t>(dk) * (dk + 1) * sizeof(float);
+    const int p_in_shared = with_p <= 160 * 1024 ? 1 : 0;
+    if (p_in_shared) shared = with_p;
+    static lb::OncePerDevice once;
+    lb::allow_shared_memory(once, lb::gdr_chunk_propagate_kernel, 160 * 1024);
+    lb::gdr_chunk_propagate_kernel<<<dim3(long_portions, heads, (dv + 31) / 32), dim3(32, 32), shared, stream>>>(
+        chunk_state, chunk_in, state, long_table, segment_slot, heads, dk, dv, num_slots, p_in_shared);
+    const int tiles_per_chunk = (chunk_tokens + lb::kReadoutTokens - 1) / lb::kReadoutTokens;
+    lb::gdr_chunk_readout_kernel<<<dim3(chunks * tiles_per_chunk, heads), 128, static_cast<size_t>(lb::kReadoutTokens) * dk * sizeof(float), stream>>>(
+        wide, chunk_in, chunk_start, chunk_length, tiles_per_chunk, out, heads, dk, dv);
     return LB_LAUNCH_RESULT();
 }
 

@@ -151,9 +151,9 @@ def test_long_portions(models, name, dtype):
     """Portions long enough for the recurrence to run them as chunks side by side, beside a short request, then decoding."""
     folder, weights = models[name]
     config = CONFIGS[name]
-    requests = {"a": tokens_for(config, 1100, 41), "b": tokens_for(config, 30, 42)}
-    schedule = [[("a", 600), ("b", 5)], [("a", 1), ("b", 20)], [("a", 490), ("b", 1)], [("b", 4), ("a", 9)]]
-    engine = load_engine(folder, dtype, max_tokens=2048)
+    requests = {"a": tokens_for(config, 1900, 41), "b": tokens_for(config, 30, 42)}
+    schedule = [[("a", 1000), ("b", 5)], [("a", 1), ("b", 20)], [("a", 890), ("b", 1)], [("b", 4), ("a", 9)]]
+    engine = load_engine(folder, dtype, max_tokens=4096)
     got = run_schedule(engine, requests, schedule)
     for key, tokens in requests.items():
         assert close_enough(got[key], plain.forward(config, weights, tokens), dtype), key
@@ -361,13 +361,13 @@ def test_tensor_core_attention_with_kept_first_keys(window, keep_first, special,
     assert worst.max() < 0.5, (int(worst.argmax()), float(worst.max()))
 
 
-LONG_STEPS = [{0: 3, 1: 1}, {0: 500, 1: 20}, {0: 1, 1: 2}, {1: 14, 0: 385}, {0: 11}]   # portions long enough to run as chunks, a last chunk of one token
+LONG_STEPS = [{0: 3, 1: 1}, {0: 1000, 1: 20}, {0: 1, 1: 2}, {1: 14, 0: 769}, {0: 27}]   # portions long enough to run as chunks, a last chunk of one token
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,groups,dk,dv,taps,steps", [
     (2, 1, 16, 32, 3, None), (3, 3, 40, 24, 1, None), (2, 2, 72, 16, 4, None), (4, 2, 128, 64, 2, None), (1, 1, 160, 40, 3, None),
-    (2, 1, 16, 32, 3, LONG_STEPS), (2, 2, 64, 128, 4, LONG_STEPS), (3, 1, 40, 20, 2, LONG_STEPS), (1, 1, 128, 72, 3, LONG_STEPS)])
+    (2, 1, 16, 32, 3, LONG_STEPS), (2, 2, 64, 128, 4, LONG_STEPS), (3, 1, 18, 40, 2, LONG_STEPS), (1, 1, 128, 72, 3, LONG_STEPS)])
 def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, dv, taps, steps, dtype):
     """Two requests in different slots, cut differently, a far write that must survive hundreds of decays close to one;
     with long portions, which run as chunks side by side from zero states and are put together afterwards."""
@@ -375,7 +375,7 @@ def test_gated_delta_rule_in_portions_against_the_recurrence(heads, groups, dk, 
 
     generator = np.random.default_rng(dk * dv + taps)
     channels = 2 * groups * dk + heads * dv
-    lengths = {0: 150, 1: 37} if steps is None else {0: 900, 1: 37}
+    lengths = {0: 150, 1: 37} if steps is None else {0: 1800, 1: 37}
     proj = {r: torch.from_numpy(generator.standard_normal((n, channels + heads))).to(dtype) for r, n in lengths.items()}
     low = {r: torch.from_numpy(generator.standard_normal((n, heads * (dk + dv)))).to(dtype) for r, n in lengths.items()}
     conv = torch.from_numpy(0.6 * generator.standard_normal((channels, taps))).float()
