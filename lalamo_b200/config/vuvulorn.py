@@ -127,7 +127,7 @@ class VuvulornConfig:
         rot_dims = _get(left, "rot.dims", int, at)
         if rot_dims < 0 or rot_dims % 2 or rot_dims > dim:
             raise ConfigError(f"{at}.rot.dims", f"must be even and at most dim={dim}, got {rot_dims}")
-        keep_first = _get(left, "mask.keep_first", int, at)
+        keep_first = _get(left, "mask.keep_first", int, at) if isinstance(left.get("mask"), Mapping) and left["mask"].get("keep_first") is not None else 0
         if keep_first < 0:
             raise ConfigError(f"{at}.mask.keep_first", f"must not be negative, got {keep_first}")
         attention = AttentionSpec(
@@ -177,8 +177,10 @@ class VuvulornConfig:
         if mlp_kind == "dense":
             ffn: Any = GatedMLPSpec(model_dim=width, hidden_dim=_positive(mlp, "ff", at), activation="silu")
         elif mlp_kind == "moe":
-            experts, count = _positive(mlp, "router.experts", at), _positive(mlp, "router.groups.count", at)
-            keep, top = _positive(mlp, "router.groups.keep", at), _positive(mlp, "router.top", at)
+            experts, top = _positive(mlp, "router.experts", at), _positive(mlp, "router.top", at)
+            grouped = isinstance(mlp.get("router"), Mapping) and mlp["router"].get("groups") is not None   # no groups: one group, kept
+            count = _positive(mlp, "router.groups.count", at) if grouped else 1
+            keep = _positive(mlp, "router.groups.keep", at) if grouped else 1
             if experts % count:
                 raise ConfigError(f"{at}.router.groups.count", f"{count} does not divide experts={experts}")
             if keep > count:

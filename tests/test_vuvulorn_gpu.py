@@ -82,7 +82,7 @@ def close_enough(got: np.ndarray, want: np.ndarray, dtype: str) -> bool:
 
 # ----------------------------------------------------------------------------- whole models
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_a_prompt_at_once_and_token_by_token(models, name, dtype):
     folder, weights = models[name]
     config = CONFIGS[name]
@@ -101,7 +101,7 @@ def test_a_prompt_at_once_and_token_by_token(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_portions_of_every_size(models, name, dtype):
     folder, weights = models[name]
     config = CONFIGS[name]
@@ -115,7 +115,7 @@ def test_portions_of_every_size(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_mixed_batches_with_pages_and_slots_used_again(models, name, dtype):
     """Up to four live requests of unequal lengths, portions beside single tokens; requests end and others take their
     slots and pages (which were overwritten with NaN when they were given back); a pool smaller than the sum."""

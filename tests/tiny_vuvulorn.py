@@ -69,7 +69,19 @@ CONFIG_R = {
     ],
 }
 
-CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R}
+# S: sizes that fit no kernel's favourite shape: a width and a vocabulary that are multiples of nothing, heads of 12, 20 and 10
+# channels, three experts, a feed-forward of 30 columns.
+CONFIG_S = {
+    "architecture": "Vuvulorn", "vocab": 97, "width": 100, "norm": {"eps": 1e-6},
+    "layers": [
+        layer(mixer(heads=2, kv_heads=1, dim=24, vdim=12, window=6, keep_first=2, rot_dims=10, scale=0.3, r_heads=2, r_kv_heads=1, r_dim=20, r_vdim=12, conv=3,
+                    decay_rank=7, gate_rank=3), moe(30, 3, 2, 1, 1)),
+        layer(mixer(heads=3, kv_heads=3, dim=10, vdim=10, window=9, keep_first=0, rot_dims=6, scale=0.4, r_heads=3, r_kv_heads=3, r_dim=10, r_vdim=6, conv=2,
+                    decay_rank=33, gate_rank=40), dense(30)),
+    ],
+}
+
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "S": CONFIG_S}
 
 
 def tensor_shapes(config: dict) -> dict[str, tuple[int, ...]]:
