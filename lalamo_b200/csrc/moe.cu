@@ -41,11 +41,13 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
     const T* row = x + static_cast<size_t>(token) * width;
     if (row_floats > 0) {
         // the token's row once into shared memory (32-bit), then four experts' rows at a time, 16 bytes a lane and turn
+#pragma unroll 8
         for (int d = lane; d < width; d += 32) x_s[d] = to_float(row[d]);
         __syncwarp();
         for (int e0 = 0; e0 < experts; e0 += 4) {
             float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            for (int c = 4 * lane; c < width; c += 128) {
+#pragma unroll 4
+            for (int c = 4 * lane; c < width; c += 128) {   // sixteen loads of the router's rows on their way at a time
                 const float4 xv = *reinterpret_cast<const float4*>(x_s + c);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {

@@ -197,6 +197,9 @@ class StepInputs:
     # the device (int32, uploaded with the rest of the description) and as the host made them.
     plans: dict[object, dict[str, torch.Tensor]] = field(default_factory=dict)
     host_plans: dict[object, dict[str, np.ndarray]] = field(default_factory=dict)
+    # What a block leaves for the block after it within this step (for instance the residual stream rounded to the
+    # activation type, by a kernel that had it in registers anyway): name -> value.
+    carry: dict[str, object] = field(default_factory=dict)
 
     def plan_of(self, part: "Part") -> tuple[dict[str, torch.Tensor], dict[str, np.ndarray]]:
         """The arrays ``part.plan_step`` made for this step: ``(on the device, on the host)``."""

@@ -122,8 +122,11 @@ class OutputNormBlock(Block):
         if pending is not None:
             ops.residual_add(residual, pending)
         runtime = self.runtime
+        carried = step.carry.pop("rounded_stream", None)   # (the stream it is a copy of, the copy), left by the block before
         if runtime.dtype == torch.float32:
             x = residual  # the sublayers read the stream in place; what they return is added only after they have read it
+        elif pending is None and carried is not None and carried[0] is residual:
+            x = carried[1]
         else:
             x = runtime.empty(*residual.shape)
             ops.cast_rows(residual, x)
@@ -131,13 +134,15 @@ class OutputNormBlock(Block):
         if isinstance(mixed, ops.SlicedSum):
             mixed = mixed.sum()
         has_ffn = self.ffn is not None
-        rounded = x if has_ffn and x is not residual else None
+        rounded = x if x is not residual else None   # the kernel that adds to the stream also rounds it for the next reader
         self._accumulate(self.mixer_norm, residual, mixed, rounded)
         if has_ffn:
             out = self.ffn.forward(x, step)
             if isinstance(out, ops.SlicedSum):
                 out = out.sum()
-            self._accumulate(self.ffn_norm, residual, out, None)
+            self._accumulate(self.ffn_norm, residual, out, rounded)
+        if rounded is not None:
+            step.carry["rounded_stream"] = (residual, rounded)
         return None
 
     @staticmethod
