@@ -241,6 +241,7 @@ __global__ void feed_tokens_kernel(int* __restrict__ token_ids, const int* __res
 // stream itself and not a norm of it.
 template <typename T>
 __global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count) {
+    allow_next_kernel();   // a product launched to start early may ask for its weights meanwhile (it waits for this kernel's end before it reads)
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < count) out[i] = from_float<T>(x[i]);
 }
@@ -262,6 +263,7 @@ __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __
                                        const T* __restrict__ b, const float* __restrict__ bias_b, float scale_b,
                                        const float* __restrict__ weight, T* __restrict__ rounded, int dim, float eps, float scale_offset) {
     extern __shared__ float shared[];
+    allow_next_kernel();   // as in cast_rows_kernel
     float* row_cache = shared;       // dim floats
     float* scratch = shared + dim;   // 33 floats
     const size_t base = static_cast<size_t>(blockIdx.x) * dim;

@@ -45,13 +45,15 @@ __device__ __forceinline__ float conv_silu(const T* __restrict__ proj, int proj_
 //   q_out, k_out [tokens, groups, dk], v_out [tokens, heads, dv], beta_out [tokens, heads], g_out [tokens, heads, dk]: 32-bit
 template <typename T>
 __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, const T* __restrict__ ag, int ag_width,
-                                   const T* __restrict__ conv_state, const float* __restrict__ conv_weight,
+                                   T* __restrict__ conv_state, const float* __restrict__ conv_weight,
                                    const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                                    float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
                                    float* __restrict__ beta_out, float* __restrict__ g_out,
                                    const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                    const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv, int taps,
-                                   int num_slots, float unit_eps, float q_scale, int* status) {
+                                   int num_slots, float unit_eps, float q_scale, int update_state, int* status) {
+    // update_state: every portion of the step is one token, and the lane that convolves a channel (the only reader of that
+    // channel's rows in the slot) also shifts the rows and appends the token's input; no state kernel runs after this one.
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int segment = token_segment[token];
@@ -62,8 +64,13 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
         return;
     }
     const int channels = 2 * groups * dk + heads * dv;
-    const T* state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
+    T* state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
     const int rel = token - start;
+    auto shift_state = [&](int ch) {
+        if (!update_state || taps <= 1) return;
+        for (int i = 0; i + 2 < taps; ++i) state_rows[static_cast<size_t>(i) * channels + ch] = state_rows[static_cast<size_t>(i + 1) * channels + ch];
+        state_rows[static_cast<size_t>(taps - 2) * channels + ch] = proj[static_cast<size_t>(token) * proj_width + ch];
+    };
     const int units = 2 * groups + 2 * heads;
     for (int unit = blockIdx.y * warps + warp; unit < units; unit += gridDim.y * warps) {
         if (unit < 2 * groups) {
@@ -80,6 +87,7 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
                 if (c < dk) {
                     values[i] = conv_silu(proj, proj_width, state_rows, channels, conv_weight, start, rel, taps, ch0 + c);
                     sum += values[i] * values[i];
+                    shift_state(ch0 + c);
                 }
             }
             sum = warp_sum(sum);
@@ -94,7 +102,10 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
             const int head = unit - 2 * groups;
             const int ch0 = 2 * groups * dk + head * dv;
             float* dst = v_out + (static_cast<size_t>(token) * heads + head) * dv;
-            for (int c = lane; c < dv; c += 32) dst[c] = conv_silu(proj, proj_width, state_rows, channels, conv_weight, start, rel, taps, ch0 + c);
+            for (int c = lane; c < dv; c += 32) {
+                dst[c] = conv_silu(proj, proj_width, state_rows, channels, conv_weight, start, rel, taps, ch0 + c);
+                shift_state(ch0 + c);
+            }
         } else {
             const int head = unit - 2 * groups - heads;
             const float rate = expf(a_log[head]);
@@ -320,6 +331,7 @@ gdr_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
 template <typename T>
 __global__ void gdr_output_kernel(const float* __restrict__ o, const T* __restrict__ ag, int ag_width, int gate_offset,
                                   const float* __restrict__ norm_weight, T* __restrict__ out, int heads, int dv, float eps) {
+    allow_next_kernel();   // the out-projection, launched to start early, may ask for its weights meanwhile
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int head = blockIdx.y * warps + warp; head < heads; head += gridDim.y * warps) {
@@ -474,18 +486,18 @@ inline void launch_scan(dim3 grid, cudaStream_t stream, const float* q, const fl
 
 extern "C" {
 
-int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_width, const void* conv_state, const float* conv_weight,
+int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_width, void* conv_state, const float* conv_weight,
                    const float* a_log, const float* dt_bias, float* q_out, float* k_out, float* v_out, float* beta_out, float* g_out,
                    const int* token_segment, const int* segment_start, const int* segment_slot, int tokens, int heads, int groups, int dk,
-                   int dv, int taps, int num_slots, float unit_eps, float q_scale, int dtype, int* status, cudaStream_t stream) {
+                   int dv, int taps, int num_slots, float unit_eps, float q_scale, int dtype, int* status, cudaStream_t stream, int update_state) {
     if (tokens == 0) return 0;
     if (dk > 32 * lb::kPrepareMaxPerLane || taps < 1 || heads % groups != 0) return -2;
     LB_DISPATCH_DTYPE(dtype, {
         const int units = 2 * groups + 2 * heads;
         lb::gdr_prepare_kernel<T><<<dim3(tokens, (units + 3) / 4), 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
-                                                              static_cast<const T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
+                                                              static_cast<T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
                                                               g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
-                                                              unit_eps, q_scale, status);
+                                                              unit_eps, q_scale, update_state, status);
     })
     return LB_LAUNCH_RESULT();
 }

@@ -800,12 +800,13 @@ def gated_delta_rule(
     beta = torch.empty(tokens, num_heads, dtype=torch.float32, device=device)
     decay = torch.empty(tokens, num_heads, key_dim, dtype=torch.float32, device=device)
     lib = _lib()
+    single_tokens = segments == tokens   # every portion is one token: the convolutions' kernel also writes their new state
     code = lib.lb_gdr_prepare(_ptr(proj), c_int(proj.shape[1]), _ptr(low_rank), c_int(low_rank.shape[1]), _ptr(conv_state), _ptr(conv_weight), _ptr(a_log),
                               _ptr(dt_bias), _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(token_segment), _ptr(segment_start), _ptr(segment_slot),
                               c_int(tokens), c_int(num_heads), c_int(num_groups), c_int(key_dim), c_int(value_dim), c_int(taps), c_int(num_slots),
-                              c_float(unit_eps), c_float(key_dim ** -0.5), c_int(dtype_code(proj.dtype)), _ptr(status), _stream())
+                              c_float(unit_eps), c_float(key_dim ** -0.5), c_int(dtype_code(proj.dtype)), _ptr(status), _stream(), c_int(1 if single_tokens else 0))
     _done(code, "gdr_prepare")
-    if taps > 1:
+    if taps > 1 and not single_tokens:
         code = lib.lb_gdr_conv_state(_ptr(proj), c_int(proj.shape[1]), _ptr(conv_state), _ptr(segment_start), _ptr(segment_length), _ptr(segment_slot),
                                      c_int(segments), c_int(channels), c_int(taps), c_int(num_slots), c_int(dtype_code(proj.dtype)), _stream())
         _done(code, "gdr_conv_state")
