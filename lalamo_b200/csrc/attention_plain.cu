@@ -199,6 +199,17 @@ __global__ void qk_norm_rope_write_token_kernel(const T* __restrict__ qkv, T* __
     }
 }
 
+// v + bias on eight bfloat16 values held in 16 bytes (the sum in 32-bit, rounded once).
+__device__ __forceinline__ uint4 add_bias_8(uint4 raw, const float* __restrict__ bias8) {
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 two = __bfloat1622float2(pairs[i]);
+        pairs[i] = __floats2bfloat162_rn(two.x + bias8[2 * i], two.y + bias8[2 * i + 1]);
+    }
+    return raw;
+}
+
 // The same work for bfloat16 and head sizes 16, 32, 64 and 128 with rotary_dim a multiple of 16: one
 // block per token, one thread per 8 consecutive channels of a head (16-byte loads and stores), so that
 // the 2, 4, 8 or 16 threads of a head are neighbours in a warp: the sum of squares is reduced and the
@@ -210,7 +221,7 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
                                                  float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
                                                  const int* __restrict__ positions, const int* __restrict__ token_segment,
                                                  const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
-                                                 int* status) {
+                                                 const float* __restrict__ bias, int* status) {
     using T = __nv_bfloat16;
     extern __shared__ float rotation[];   // cos[half], sin[half]
     const int token = blockIdx.x;
@@ -242,6 +253,10 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
             const float2 two = __bfloat1622float2(pairs[i]);
             own[2 * i] = two.x;
             own[2 * i + 1] = two.y;
+        }
+        if (bias != nullptr) {   // added in 32-bit, before the norm
+#pragma unroll
+            for (int i = 0; i < 8; ++i) own[i] += bias[static_cast<size_t>(unit) * hd + chunk * 8 + i];
         }
     }
     {
@@ -289,8 +304,9 @@ __global__ void qk_norm_rope_write_vector_kernel(const __nv_bfloat16* __restrict
         return;
     }
     *reinterpret_cast<uint4*>(key_row + chunk * 8) = packed;
-    const uint4 v_raw =
-        *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(token) * width + static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8);
+    const size_t v_offset = static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8;
+    uint4 v_raw = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(token) * width + v_offset);
+    if (bias != nullptr) v_raw = add_bias_8(v_raw, bias + v_offset);
     const T* v_values = reinterpret_cast<const T*>(&v_raw);
 #pragma unroll
     for (int i = 0; i < 8; ++i) value[static_cast<size_t>(chunk * 8 + i) * layout.page_size] = v_values[i];
@@ -307,7 +323,7 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
                                               float scale_offset, const float* __restrict__ inv_freq, int rotary_dim,
                                               const int* __restrict__ positions, const int* __restrict__ token_segment,
                                               const int* __restrict__ block_table, PagedLayout layout, int num_heads, int write_kv,
-                                              int tokens, int* status) {
+                                              int tokens, const float* __restrict__ bias, int* status) {
     static_assert(RUN == 4 || RUN == 8, "a channel's rows leave as one 8- or 16-byte store");
     using T = __nv_bfloat16;
     extern __shared__ float rotation[];   // per token of the run: cos[half], sin[half]
@@ -333,6 +349,14 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
             raw[t] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(unit) * hd + chunk * 8);
             if (writes_values) v_raw[t] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8);
         }
+    }
+    float own_bias[8];   // of this thread's eight query or key channels, added in 32-bit before the norm
+#pragma unroll
+    for (int i = 0; i < 8; ++i) own_bias[i] = active && bias != nullptr ? bias[static_cast<size_t>(unit) * hd + chunk * 8 + i] : 0.0f;
+    if (writes_values && bias != nullptr) {
+        const float* value_bias = bias + static_cast<size_t>(num_heads + layout.num_groups + group) * hd + chunk * 8;
+#pragma unroll
+        for (int t = 0; t < RUN; ++t) v_raw[t] = add_bias_8(v_raw[t], value_bias);
     }
     // (the loads above are on their way while the sines and cosines are worked out)
     for (int i = threadIdx.x; i < count * half; i += blockDim.x) {
@@ -361,8 +385,8 @@ __global__ void qk_norm_rope_write_run_kernel(const __nv_bfloat16* __restrict__ 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 two = __bfloat1622float2(pairs[i]);
-            own[2 * i] = two.x;
-            own[2 * i + 1] = two.y;
+            own[2 * i] = two.x + own_bias[2 * i];
+            own[2 * i + 1] = two.y + own_bias[2 * i + 1];
         }
         float sum = 0.0f;
 #pragma unroll
@@ -543,7 +567,7 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2 != 0) return -2;
     if (value_dim <= 0) value_dim = head_dim;
     lb::PagedLayout layout{page_size, num_pages, max_blocks, num_groups, head_dim, value_dim};
-    const bool plain_layout = value_dim == head_dim && bias == nullptr;   // what the 16-byte kernels below take
+    const bool plain_layout = value_dim == head_dim;   // what the 16-byte kernels below take
     const bool power_of_two_head = head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128;
     const int vector_threads = (((num_heads + num_groups) * (head_dim / 8)) + 31) / 32 * 32;
     if (tokens > 64 && plain_layout && dtype == lb::kBFloat16 && power_of_two_head && rotary_dim % 16 == 0 && rotary_dim <= head_dim && vector_threads <= 1024 &&
@@ -554,13 +578,13 @@ int lb_qk_norm_rope_write(const void* qkv, void* q_out, void* k_pages, void* v_p
             lb::qk_norm_rope_write_run_kernel<kRun><<<(tokens + kRun - 1) / kRun, vector_threads, kRun * shared, stream>>>(
                 static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
                 static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
-                layout, num_heads, write_kv, tokens, status);
+                layout, num_heads, write_kv, tokens, bias, status);
             return LB_LAUNCH_RESULT();
         }
         lb::qk_norm_rope_write_vector_kernel<<<tokens, vector_threads, shared, stream>>>(
             static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pages),
             static_cast<__nv_bfloat16*>(v_pages), q_weight, k_weight, eps, scale_offset, inv_freq, rotary_dim, positions, token_segment, block_table,
-            layout, num_heads, write_kv, status);
+            layout, num_heads, write_kv, bias, status);
         return LB_LAUNCH_RESULT();
     }
     if (tokens > 64) {

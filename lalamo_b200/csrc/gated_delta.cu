@@ -10,6 +10,8 @@
 // request was cut into steps or on what else is in the batch.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace lb {
 
 constexpr int kPrepareMaxPerLane = 16;   // key_dim <= 512
@@ -43,17 +45,18 @@ __device__ __forceinline__ float conv_silu(const T* __restrict__ proj, int proj_
 //   proj [tokens, proj_width]: q (groups x dk) | k (groups x dk) | v (heads x dv) | b (heads) | unused
 //   ag   [tokens, ag_width]:   a (heads x dk) | ...
 //   q_out, k_out [tokens, groups, dk], v_out [tokens, heads, dv], beta_out [tokens, heads], g_out [tokens, heads, dk]: 32-bit
-template <typename T>
+template <typename T, bool UPDATE>
 __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, const T* __restrict__ ag, int ag_width,
-                                   T* __restrict__ conv_state, const float* __restrict__ conv_weight,
+                                   std::conditional_t<UPDATE, T*, const T* __restrict__> conv_state, const float* __restrict__ conv_weight,
                                    const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                                    float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
                                    float* __restrict__ beta_out, float* __restrict__ g_out,
                                    const int* __restrict__ token_segment, const int* __restrict__ segment_start,
                                    const int* __restrict__ segment_slot, int heads, int groups, int dk, int dv, int taps,
-                                   int num_slots, float unit_eps, float q_scale, int update_state, int* status) {
-    // update_state: every portion of the step is one token, and the lane that convolves a channel (the only reader of that
+                                   int num_slots, float unit_eps, float q_scale, int* status) {
+    // UPDATE: every portion of the step is one token, and the lane that convolves a channel (the only reader of that
     // channel's rows in the slot) also shifts the rows and appends the token's input; no state kernel runs after this one.
+    // (Otherwise the state is read-only here, and says so: the loads were a third slower without it.)
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int segment = token_segment[token];
@@ -64,12 +67,14 @@ __global__ void gdr_prepare_kernel(const T* __restrict__ proj, int proj_width, c
         return;
     }
     const int channels = 2 * groups * dk + heads * dv;
-    T* state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
+    auto state_rows = conv_state + static_cast<size_t>(slot) * (taps > 1 ? taps - 1 : 0) * channels;
     const int rel = token - start;
     auto shift_state = [&](int ch) {
-        if (!update_state || taps <= 1) return;
-        for (int i = 0; i + 2 < taps; ++i) state_rows[static_cast<size_t>(i) * channels + ch] = state_rows[static_cast<size_t>(i + 1) * channels + ch];
-        state_rows[static_cast<size_t>(taps - 2) * channels + ch] = proj[static_cast<size_t>(token) * proj_width + ch];
+        if constexpr (UPDATE) {
+            if (taps <= 1) return;
+            for (int i = 0; i + 2 < taps; ++i) state_rows[static_cast<size_t>(i) * channels + ch] = state_rows[static_cast<size_t>(i + 1) * channels + ch];
+            state_rows[static_cast<size_t>(taps - 2) * channels + ch] = proj[static_cast<size_t>(token) * proj_width + ch];
+        }
     };
     const int units = 2 * groups + 2 * heads;
     for (int unit = blockIdx.y * warps + warp; unit < units; unit += gridDim.y * warps) {
@@ -494,10 +499,17 @@ int lb_gdr_prepare(const void* proj, int proj_width, const void* ag, int ag_widt
     if (dk > 32 * lb::kPrepareMaxPerLane || taps < 1 || heads % groups != 0) return -2;
     LB_DISPATCH_DTYPE(dtype, {
         const int units = 2 * groups + 2 * heads;
-        lb::gdr_prepare_kernel<T><<<dim3(tokens, (units + 3) / 4), 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
-                                                              static_cast<T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
-                                                              g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
-                                                              unit_eps, q_scale, update_state, status);
+        const dim3 grid(tokens, (units + 3) / 4);
+        if (update_state)
+            lb::gdr_prepare_kernel<T, true><<<grid, 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
+                                                                       static_cast<T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out, g_out,
+                                                                       token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots, unit_eps,
+                                                                       q_scale, status);
+        else
+            lb::gdr_prepare_kernel<T, false><<<grid, 128, 0, stream>>>(static_cast<const T*>(proj), proj_width, static_cast<const T*>(ag), ag_width,
+                                                                        static_cast<const T*>(conv_state), conv_weight, a_log, dt_bias, q_out, k_out, v_out, beta_out,
+                                                                        g_out, token_segment, segment_start, segment_slot, heads, groups, dk, dv, taps, num_slots,
+                                                                        unit_eps, q_scale, status);
     })
     return LB_LAUNCH_RESULT();
 }
