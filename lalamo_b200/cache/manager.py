@@ -2,7 +2,8 @@
 rule, and slots for per-request state of fixed size.
 
 * Every schedule entry whose mixer declares a :class:`PagedKVNeed` gets its own key and value
-  tensors ``[pages, page_size, groups, head_dim]``.  Entries with the same retention rule (all
+  tensors ``[pages, page_size, groups, head_dim]`` (keys only where the need says ``values_in_keys``: a mixer whose
+  tokens leave one row behind, from which keys and values are both made).  Entries with the same retention rule (all
   keys, or a window of ``w`` with the first ``f`` positions kept) form a *group*: one page pool and
   one block table per request serve the whole group, since such layers hold the same positions.
   Groups have pages of their own.
@@ -167,7 +168,8 @@ class CacheManager:
                     assert isinstance(need, PagedKVNeed)
                     # keys [page][row][group][channel]; values transposed, [page][group][channel][row]
                     self.k_pages[entry] = torch.zeros((num_pages, page_size, need.num_groups, need.head_dim), dtype=runtime.dtype, device=runtime.device)
-                    self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.value_dim or need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
+                    if not need.values_in_keys:
+                        self.v_pages[entry] = torch.zeros((num_pages, need.num_groups, need.value_dim or need.head_dim, page_size), dtype=runtime.dtype, device=runtime.device)
             for entry in self.layout.slot_entries:
                 need = needs[entry]
                 assert isinstance(need, SlotStateNeed)
@@ -203,7 +205,8 @@ class CacheManager:
         index = torch.tensor(pages, dtype=torch.long, device=self.runtime.device)
         for entry in self.groups[group_index].entries:
             self.k_pages[entry][index] = float("nan")
-            self.v_pages[entry][index] = float("nan")
+            if entry in self.v_pages:
+                self.v_pages[entry][index] = float("nan")
 
     # --------------------------------------------------------------------- requests
     def admit(self, request_id: object) -> RequestCache:
@@ -329,7 +332,7 @@ class CacheManager:
             owns = owner == entry
             group = self.layout.entry_group[entry]
             if group is not None:
-                result.append(PagedKVView(owns, self.k_pages[owner], self.v_pages[owner], block_tables[group]))
+                result.append(PagedKVView(owns, self.k_pages[owner], self.v_pages.get(owner), block_tables[group]))
             else:
                 result.append(SlotStateView(owns, self.states[owner], segment_slot))
         return result
@@ -341,8 +344,8 @@ class CacheManager:
         for index, group in enumerate(self.groups):
             live = record.length if group.window is None else min(record.length, group.window + group.keep_first)
             for entry in group.entries:
-                pages, values = self.k_pages[entry], self.v_pages[entry]
-                total += live * pages.shape[2] * (pages.shape[3] + values.shape[2]) * pages.element_size()
+                pages, values = self.k_pages[entry], self.v_pages.get(entry)
+                total += live * pages.shape[2] * (pages.shape[3] + (values.shape[2] if values is not None else 0)) * pages.element_size()
         for state in self.states.values():
             total += state[0].numel() * state.element_size()
         return total

@@ -8,6 +8,7 @@ from .plan import (
     FeedForwardSpec,
     GatedDeltaSpec,
     GatedMLPSpec,
+    LatentAttentionSpec,
     MixerSpec,
     ModelPlan,
     NormSpec,
@@ -17,14 +18,17 @@ from .plan import (
     RMSNormSpec,
     RopeSpec,
     RoutedMLPSpec,
+    SandwichBlockSpec,
     ScheduleEntry,
     ShortConvSpec,
 )
+from .tudulix import TudulixConfig
 from .vuvulorn import VuvulornConfig
 from .registry import architectures, config_from_dict, load_config, register_architecture
 
 register_architecture("Lfm2ForCausalLM", Lfm2Config)
 register_architecture("Vuvulorn", VuvulornConfig)
+register_architecture("Tudulix", TudulixConfig)
 
 __all__ = [
     "AttentionSpec",
@@ -33,6 +37,7 @@ __all__ = [
     "FeedForwardSpec",
     "GatedDeltaSpec",
     "GatedMLPSpec",
+    "LatentAttentionSpec",
     "Lfm2Config",
     "MixerSpec",
     "ModelPlan",
@@ -43,8 +48,10 @@ __all__ = [
     "RMSNormSpec",
     "RopeSpec",
     "RoutedMLPSpec",
+    "SandwichBlockSpec",
     "ScheduleEntry",
     "ShortConvSpec",
+    "TudulixConfig",
     "UnknownArchitectureError",
     "VuvulornConfig",
     "architectures",

@@ -24,6 +24,7 @@ __all__ = [
     "FeedForwardSpec",
     "GatedDeltaSpec",
     "GatedMLPSpec",
+    "LatentAttentionSpec",
     "MixerSpec",
     "ModelPlan",
     "NormSpec",
@@ -33,6 +34,7 @@ __all__ = [
     "RMSNormSpec",
     "RopeSpec",
     "RoutedMLPSpec",
+    "SandwichBlockSpec",
     "ScheduleEntry",
     "ShortConvSpec",
 ]
@@ -57,6 +59,9 @@ class RMSNormSpec(NormSpec):
     dim: int = 0
     eps: float = 1e-5
     scale_offset: float = 0.0
+    # True: the whole norm in 32-bit, ``x * rsqrt(mean(x^2) + eps) * (w + scale_offset)`` rounded once to the
+    # activation type (False: the normalised value and the scale are each rounded first, as the reference does).
+    exact: bool = False
 
 
 @dataclass(frozen=True)
@@ -66,12 +71,15 @@ class PositionSpec:
 
 @dataclass(frozen=True)
 class RopeSpec(PositionSpec):
-    """Unscaled rotary embedding over the first ``rotary_dim`` channels of a head,
-    rotate-half (NeoX) pairing (``lalamo/modules/rope.py:58-102``)."""
+    """Unscaled rotary embedding over the first ``rotary_dim`` channels of a head
+    (``lalamo/modules/rope.py:58-102``).  ``pairing``: ``"half"`` rotates channel ``i`` with channel
+    ``i + rotary_dim / 2`` (NeoX), ``"interleaved"`` channel ``2i`` with ``2i + 1``; pair ``i`` turns by
+    ``position * theta ** (-2i / rotary_dim)`` either way."""
 
     kind: ClassVar[str] = "rope"
     rotary_dim: int = 0
     theta: float = 10000.0
+    pairing: str = "half"
 
 
 @dataclass(frozen=True)
@@ -96,6 +104,29 @@ class AttentionSpec(MixerSpec):
     value_dim: int | None = None  # size of a value head; None -> head_dim
     keep_first: int = 0  # under a window, the first tokens of a request that stay visible (at their true positions)
     has_bias: bool = False  # biases on the q, k, v and output projections
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Causal attention whose keys and values are made from one latent vector per token: ``c = norm(W_down h)[:latent_dim]``
+    (RMS norm with a plain weight) and one rotated key part ``r = rope(W_down h)[latent_dim:]`` of ``rope_dim`` channels
+    shared by all heads; per head the unrotated key is ``W_uk c`` (``head_dim`` channels), the value ``W_uv c``
+    (``value_dim``); a query head is ``[head_dim unrotated, rope_dim rotated]``; the score is
+    ``(q_plain . k_plain + q_rot . r) * scale``.  Only ``c`` and ``r`` are cached.  ``gated``: the heads' outputs are
+    multiplied by ``sigmoid(W_gate h)`` before the out-projection."""
+
+    kind: ClassVar[str] = "latent_attention"
+    model_dim: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    rope_dim: int = 0
+    value_dim: int = 0
+    latent_dim: int = 0
+    latent_norm: NormSpec | None = None
+    position: PositionSpec | None = None
+    window: int | None = None
+    scale: float | None = None  # None -> (head_dim + rope_dim) ** -0.5
+    gated: bool = False
 
 
 @dataclass(frozen=True)
@@ -149,12 +180,14 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec(FeedForwardSpec):
-    """``down(up(x) * act(gate(x)))`` (``lalamo/modules/mlp.py:233-262``)."""
+    """``down(up(x) * act(gate(x)))`` (``lalamo/modules/mlp.py:233-262``).  With ``activation="sigmoid_limit"`` the hidden
+    value is ``g * sigmoid(1.702 g) * (u + 1)`` for ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``."""
 
     kind: ClassVar[str] = "gated_mlp"
     model_dim: int = 0
     hidden_dim: int = 0
     activation: str = "silu"
+    limit: float = 0.0  # of the "sigmoid_limit" activation
 
 
 @dataclass(frozen=True)
@@ -162,7 +195,11 @@ class RoutedMLPSpec(FeedForwardSpec):
     """A mixture of ``num_experts`` gated feed-forward layers of width ``hidden_dim`` of which each token
     uses ``top``: router scores ``score(W_router h)`` in 32-bit; experts in ``group_count`` equal groups of
     neighbours, a group scored by the sum of its two largest scores, only the best ``group_keep`` groups
-    eligible; the chosen scores (over their sum if ``renormalize``) weigh the experts' outputs."""
+    eligible; the chosen scores (over their sum if ``renormalize``) weigh the experts' outputs.
+    ``router_bias``: a bias on the router's logits.  ``score="logits"`` ranks experts by the logits themselves;
+    ``chosen_softmax``: the weights are the softmax over the chosen scores only.  ``limit``: of the experts'
+    ``"sigmoid_limit"`` activation (see :class:`GatedMLPSpec`).  ``shared``: a dense feed-forward that every token
+    runs besides, added to the experts' weighted sum."""
 
     kind: ClassVar[str] = "routed_mlp"
     model_dim: int = 0
@@ -174,6 +211,10 @@ class RoutedMLPSpec(FeedForwardSpec):
     score: str = "sigmoid"
     renormalize: bool = False
     activation: str = "silu"
+    router_bias: bool = False
+    chosen_softmax: bool = False
+    limit: float = 0.0
+    shared: GatedMLPSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -186,6 +227,20 @@ class OutputNormBlockSpec:
     ffn: FeedForwardSpec | None = None
     ffn_norm: NormSpec | None = None
     arrangement: str = "output_norm"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A block with a norm before and after each sublayer: ``x <- x + mixer_out_norm(mixer(mixer_norm(x)));
+    x <- x + ffn_out_norm(ffn(ffn_norm(x)))`` (``ffn=None``: no second half)."""
+
+    mixer_norm: NormSpec
+    mixer: MixerSpec
+    mixer_out_norm: NormSpec
+    ffn_norm: NormSpec | None = None
+    ffn: FeedForwardSpec | None = None
+    ffn_out_norm: NormSpec | None = None
+    arrangement: str = "sandwich_norm"
 
 
 @dataclass(frozen=True)
@@ -213,12 +268,13 @@ class EmbeddingSpec:
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """The read-out: logits ``x @ W.T`` in 32-bit, with ``W`` the embedding table when ``tied``."""
+    """The read-out: logits ``(x @ W.T) * scale`` in 32-bit, with ``W`` the embedding table when ``tied``."""
 
     kind: ClassVar[str] = "lm_head"
     vocab_size: int = 0
     model_dim: int = 0
     tied: bool = True
+    scale: float = 1.0  # the logits are multiplied by this (in 32-bit)
 
 
 @dataclass(frozen=True)
@@ -233,13 +289,16 @@ class ScheduleEntry:
 
     layer: int
     cache_from: int | None = None
+    # True: the embedding's output (the stream as it was before the first block) is added to the stream
+    # right before this execution (a model that runs a stretch of its layers several times re-feeds its input).
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
 class ModelPlan:
     vocab_size: int
     model_dim: int
-    layers: tuple[BlockSpec | OutputNormBlockSpec, ...]
+    layers: tuple[BlockSpec | OutputNormBlockSpec | SandwichBlockSpec, ...]
     final_norm: NormSpec
     tie_embeddings: bool = True
     embedding_scale: float | None = None

@@ -82,6 +82,16 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// Activation codes shared with the Python bindings: 0 silu, 1 gelu (exact), 2 identity (each act(gate) * up), and
+// 3, a gate with a sigmoid of fixed slope under limits on both inputs:
+//   g = min(gate, limit), u = clamp(up, -limit, limit);  hidden = g * sigmoid(1.702 g) * (u + 1)
+constexpr int kSigmoidLimit = 3;
+constexpr float kSigmoidLimitSlope = 1.702f;
+__device__ __forceinline__ float sigmoid_limit_gate(float gate, float up, float limit) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + expf(-kSigmoidLimitSlope * g)) * (u + 1.0f);
+}
+
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may
 // start while the kernel before it on the stream still runs; whatever it does before
 // `wait_for_previous_kernel()` must not depend on (or disturb) that kernel's work.  It is used to pull

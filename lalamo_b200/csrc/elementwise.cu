@@ -7,9 +7,10 @@
 namespace lb {
 
 // residual[t, :] = float(table[ids[t], :]) * scale
+// accumulate: residual[t, :] += ... instead (a model that feeds its input again further up)
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                             int dim, int vocab, float scale, int* status) {
+                             int dim, int vocab, float scale, int accumulate, int* status) {
     const int token = blockIdx.x;
     int id = ids[token];
     if (id < 0 || id >= vocab) {
@@ -18,6 +19,10 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     }
     const T* row = table + static_cast<size_t>(id) * dim;
     float* dst = out + static_cast<size_t>(token) * dim;
+    if (accumulate) {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] += to_float(row[d]) * scale;
+        return;
+    }
     if (sizeof(T) == 2 && dim % 8 == 0) {
         // eight elements per thread and turn: one 16-byte load, two 16-byte stores
         for (int d = 8 * threadIdx.x; d < dim; d += 8 * blockDim.x) {
@@ -35,14 +40,15 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // One block per output row r.  src = rows ? rows[r] : r.
 //   h = x[src] (+ delta[src]);   if write_back: x[src] = h  (x is the 32-bit residual stream)
 //   n = T(h * rsqrt(mean(h^2) + eps));   out[r] = T(n * T(w + offset))
-// The two roundings to T follow the reference's norm in its "only normalisation is upcast" mode.
+// The two roundings to T follow the reference's norm in its "only normalisation is upcast" mode; with `exact`
+// the norm is 32-bit throughout, out[r] = T(h * rsqrt(..) * (w + offset)).
 // With `slices` > 0 the delta is a product left as its K slices' partial sums: `partials[s][src][d]`, `slice_stride`
 // floats apart, added in slice order and rounded to T as the product's own epilogue would have stored it.
 template <typename TX, typename T>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials, int slices,
                                size_t slice_stride, const float* __restrict__ weight,
                                const int* __restrict__ rows, T* __restrict__ out, int dim, float eps,
-                               float scale_offset, int write_back) {
+                               float scale_offset, int write_back, int exact) {
     extern __shared__ float shared[];
     // Launched to start early: it is resident when the kernel before it ends (no launch in between).  Only then
     // may the product after it start and pull its weights towards L2: under the stream of the kernel before,
@@ -118,7 +124,13 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const T* __restrict__ delta, 
     const float total = block_sum(sum, scratch);
     const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
     T* dst = out + static_cast<size_t>(r) * dim;
-    if (kVector && dim % 4 == 0) {
+    if (exact) {
+        for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+            const float h = row_cache[d];
+            if (write_back && adds) xr[d] = from_float<TX>(h);
+            dst[d] = from_float<T>(h * inv * (weight[d] + scale_offset));
+        }
+    } else if (kVector && dim % 4 == 0) {
         for (int d = 4 * threadIdx.x; d < dim; d += 4 * blockDim.x) {
             const float4 h = *reinterpret_cast<const float4*>(row_cache + d);
             if (write_back && adds) *reinterpret_cast<float4*>(reinterpret_cast<float*>(xr) + d) = h;
@@ -166,7 +178,7 @@ __device__ __forceinline__ float activate(float v, int activation) {
 // fused[t] = [up (hidden) ; gate (hidden)];  out[t, f] = T(up * act(gate)), 32-bit inside.
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ fused, T* __restrict__ out, int hidden, size_t count,
-                                        int activation) {
+                                        int activation, float limit) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= count) return;
     const size_t token = i / hidden;
@@ -174,12 +186,12 @@ __global__ void gated_activation_kernel(const T* __restrict__ fused, T* __restri
     const T* row = fused + token * 2 * static_cast<size_t>(hidden);
     const float up = to_float(row[f]);
     const float gate = to_float(row[hidden + f]);
-    out[i] = from_float<T>(up * round_to<T>(activate(gate, activation)));
+    out[i] = activation == kSigmoidLimit ? from_float<T>(sigmoid_limit_gate(gate, up, limit)) : from_float<T>(up * round_to<T>(activate(gate, activation)));
 }
 
 // The same, eight elements per thread with 16-byte accesses (hidden % 8 == 0).
 __global__ void gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__ fused, __nv_bfloat16* __restrict__ out, int hidden,
-                                               size_t groups, int activation) {
+                                               size_t groups, int activation, float limit) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= groups) return;
     const int per_row = hidden / 8;
@@ -195,8 +207,10 @@ __global__ void gated_activation_bf16x8_kernel(const __nv_bfloat16* __restrict__
 #pragma unroll
     for (int pair = 0; pair < 4; ++pair) {
         const float2 u = __bfloat1622float2(up[pair]), g = __bfloat1622float2(gate[pair]);
-        result[pair] = __floats2bfloat162_rn(u.x * round_to<__nv_bfloat16>(activate(g.x, activation)),
-                                             u.y * round_to<__nv_bfloat16>(activate(g.y, activation)));
+        result[pair] = activation == kSigmoidLimit
+                           ? __floats2bfloat162_rn(sigmoid_limit_gate(g.x, u.x, limit), sigmoid_limit_gate(g.y, u.y, limit))
+                           : __floats2bfloat162_rn(u.x * round_to<__nv_bfloat16>(activate(g.x, activation)),
+                                                   u.y * round_to<__nv_bfloat16>(activate(g.y, activation)));
     }
     *reinterpret_cast<uint4*>(out + token * static_cast<size_t>(hidden) + f) = result_raw;
 }
@@ -257,11 +271,14 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
 //   y = scale_a * (a[r] + bias_a) + scale_b * (b[r] + bias_b)        (b and the biases may be absent)
 //   residual[r] += y * rsqrt(mean(y^2) + eps) * (w + offset)
 //   rounded[r] = T(residual[r])                                      (if asked for: the next sublayer's input)
+//   or, with next_weight: rounded[r] = T(residual[r] * rsqrt(mean(residual[r]^2) + next_eps) * (next_weight + next_offset)),
+//   the norm that the next sublayer begins with
 // Sum, statistics, norm and residual sum are 32-bit.
 template <typename T>
 __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ bias_a, float scale_a,
                                        const T* __restrict__ b, const float* __restrict__ bias_b, float scale_b,
-                                       const float* __restrict__ weight, T* __restrict__ rounded, int dim, float eps, float scale_offset) {
+                                       const float* __restrict__ weight, T* __restrict__ rounded, int dim, float eps, float scale_offset,
+                                       const float* __restrict__ next_weight, float next_eps, float next_offset) {
     extern __shared__ float shared[];
     allow_next_kernel();   // as in cast_rows_kernel
     float* row_cache = shared;       // dim floats
@@ -282,11 +299,26 @@ __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __
     }
     const float total = block_sum(sum, scratch);
     const float inv = rsqrtf(total / static_cast<float>(dim) + eps);
+    float squares = 0.0f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
         const float h = residual[base + d] + row_cache[d] * inv * (weight[d] + scale_offset);
         residual[base + d] = h;
-        if (rounded) rounded[base + d] = from_float<T>(h);
+        if (next_weight) {
+            row_cache[d] = h;   // each thread rereads only what it wrote
+            squares += h * h;
+        } else if (rounded) {
+            rounded[base + d] = from_float<T>(h);
+        }
     }
+    if (next_weight == nullptr) return;
+    const float next_inv = rsqrtf(block_sum(squares, scratch) / static_cast<float>(dim) + next_eps);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) rounded[base + d] = from_float<T>(row_cache[d] * next_inv * (next_weight[d] + next_offset));
+}
+
+// x[i] *= factor (32-bit, in place)
+__global__ void scale_kernel(float* __restrict__ x, float factor, size_t count) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < count) x[i] *= factor;
 }
 
 }  // namespace lb
@@ -311,10 +343,10 @@ int lb_fill_slots(const long long* table, int states, long long largest_bytes, i
 }
 
 int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim, int vocab, float scale, int dtype,
-             int* status, cudaStream_t stream) {
+             int* status, cudaStream_t stream, int accumulate) {
     if (tokens == 0) return 0;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::embed_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(table), ids, out, dim, vocab, scale, status);
+        lb::embed_kernel<T><<<tokens, 256, 0, stream>>>(static_cast<const T*>(table), ids, out, dim, vocab, scale, accumulate, status);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -322,7 +354,8 @@ int lb_embed(const void* table, const int* ids, float* out, int tokens, int dim,
 // x_is_float: 1 when x is the 32-bit residual stream, 0 when x has the activation type.
 // partials, slices, slice_stride: see rmsnorm_kernel (slices == 0: none); the vector path needs slice_stride % 4 == 0.
 int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials, int slices, long long slice_stride, const float* weight,
-               const int* rows, void* out, int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream) {
+               const int* rows, void* out, int out_rows, int dim, float eps, float scale_offset, int write_back, int dtype, cudaStream_t stream,
+               int exact) {
     if (out_rows == 0) return 0;
     if (slices < 0 || (slices > 0 && (partials == nullptr || slice_stride < 0 || (dim % 4 == 0 && slice_stride % 4 != 0)))) return -2;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
@@ -339,12 +372,12 @@ int lb_rmsnorm(void* x, int x_is_float, const void* delta, const float* partials
             auto kernel = lb::rmsnorm_kernel<float, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
             lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<float*>(x), static_cast<const T*>(delta), partials, slices,
-                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact);
         } else {
             auto kernel = lb::rmsnorm_kernel<T, T>;
             if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
             lb::launch_overlapped(kernel, dim3(out_rows), dim3(threads), shared, stream, static_cast<T*>(x), static_cast<const T*>(delta), partials, slices,
-                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back);
+                                  static_cast<size_t>(slice_stride), weight, rows, static_cast<T*>(out), dim, eps, scale_offset, write_back, exact);
         }
     })
     return LB_LAUNCH_RESULT();
@@ -375,18 +408,18 @@ int lb_gather_rows(const void* src, const int* rows, void* out, int out_rows, in
 }
 
 int lb_gated_activation(const void* fused, void* out, int tokens, int hidden, int activation, int dtype,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, float limit) {
     const size_t count = static_cast<size_t>(tokens) * hidden;
     if (count == 0) return 0;
     if (dtype == lb::kBFloat16 && hidden % 8 == 0) {
         const size_t groups = count / 8;
         lb::gated_activation_bf16x8_kernel<<<static_cast<unsigned>((groups + 255) / 256), 256, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(fused), static_cast<__nv_bfloat16*>(out), hidden, groups, activation);
+            static_cast<const __nv_bfloat16*>(fused), static_cast<__nv_bfloat16*>(out), hidden, groups, activation, limit);
         return LB_LAUNCH_RESULT();
     }
     const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
     LB_DISPATCH_DTYPE(dtype, {
-        lb::gated_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(fused), static_cast<T*>(out), hidden, count, activation);
+        lb::gated_activation_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(fused), static_cast<T*>(out), hidden, count, activation, limit);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -412,7 +445,9 @@ int lb_add_bias(void* x, const float* bias, int rows, int dim, int dtype, cudaSt
 
 // b, bias_a, bias_b and rounded may be null.
 int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, float scale_a, const void* b, const float* bias_b, float scale_b,
-                       const float* weight, void* rounded, int rows, int dim, float eps, float scale_offset, int dtype, cudaStream_t stream) {
+                       const float* weight, void* rounded, int rows, int dim, float eps, float scale_offset, int dtype, cudaStream_t stream,
+                       const float* next_weight, float next_eps, float next_offset) {
+    if (next_weight != nullptr && rounded == nullptr) return -2;
     if (rows == 0) return 0;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
     if (shared > 200 * 1024) return -2;
@@ -422,8 +457,14 @@ int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, floa
         auto kernel = lb::norm_accumulate_kernel<T>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         kernel<<<rows, threads, shared, stream>>>(residual, static_cast<const T*>(a), bias_a, scale_a, static_cast<const T*>(b), bias_b, scale_b, weight,
-                                                  static_cast<T*>(rounded), dim, eps, scale_offset);
+                                                  static_cast<T*>(rounded), dim, eps, scale_offset, next_weight, next_eps, next_offset);
     })
+    return LB_LAUNCH_RESULT();
+}
+
+int lb_scale(float* x, float factor, long long count, cudaStream_t stream) {
+    if (count == 0) return 0;
+    lb::scale_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(x, factor, static_cast<size_t>(count));
     return LB_LAUNCH_RESULT();
 }
 

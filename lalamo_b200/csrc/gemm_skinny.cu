@@ -31,6 +31,7 @@ struct SkinnyParams {
     int tokens, k, n;         // n: output columns (rows of one row block of W)
     int row_block_stride;     // rows between the row blocks that the epilogue combines
     int activation;
+    float limit;   // of activation 3
     // short convolution
     __nv_bfloat16* state;             // [slots, taps - 1, n]
     const float* conv_weight;         // [n, taps]
@@ -178,7 +179,9 @@ gemm_skinny_kernel(const SkinnyParams p) {
                 static_cast<float*>(p.out)[where] += round_bf16(value);
             } else {
                 const float up = round_bf16(value), gate = round_bf16(total[1][row][token]);
-                static_cast<__nv_bfloat16*>(p.out)[where] = __float2bfloat16_rn(up * round_bf16(skinny_activate(gate, p.activation)));
+                static_cast<__nv_bfloat16*>(p.out)[where] = p.activation == kSigmoidLimit
+                                                                ? __float2bfloat16_rn(sigmoid_limit_gate(total[1][row][token], value, p.limit))
+                                                                : __float2bfloat16_rn(up * round_bf16(skinny_activate(gate, p.activation)));
             }
         }
     } else {
@@ -256,7 +259,7 @@ extern "C" {
 int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, int n, int epilogue, int activation,
                    void* state, const float* conv_weight, const float* conv_bias, const int* token_segment,
                    const int* segment_start, const int* segment_length, const int* segment_slot, int segments, int taps,
-                   int num_slots, int prefetch, int* status, cudaStream_t stream) {
+                   int num_slots, int prefetch, int* status, cudaStream_t stream, float limit) {
     if (tokens == 0) return 0;
     if (tokens < 1 || tokens > 16 || k % 32 != 0 || n % 8 != 0 || k < 32) return -2;
     lb::SkinnyParams p;
@@ -268,6 +271,7 @@ int lb_gemm_skinny(const void* x, const void* w, void* out, int tokens, int k, i
     p.n = n;
     p.row_block_stride = n;
     p.activation = activation;
+    p.limit = limit;
     p.state = static_cast<__nv_bfloat16*>(state);
     p.conv_weight = conv_weight;
     p.conv_bias = conv_bias;

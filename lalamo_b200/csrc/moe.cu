@@ -20,16 +20,16 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
 }
 
 // One warp per token.
-//   z[e] = x . router[e]  (32-bit);   s[e] = sigmoid(z[e])   (score_kind 0)  or softmax(z)[e]   (score_kind 1)
+//   z[e] = x . router[e] (+ bias[e])  (32-bit);   s[e] = sigmoid(z[e])   (score_kind 0),  softmax(z)[e]   (score_kind 1)  or  z[e]  (score_kind 2)
 //   experts form `group_count` equal groups of neighbours; a group's score is the sum of its two largest s (of its
 //   only one, in groups of one); experts outside the best `group_keep` groups cannot be chosen;
 //   chosen[t, :] = the `top` eligible experts of largest s, in that order; weights[t, :] = their s (divided by their
-//   sum if `renormalize`), times `weight_scale`.
+//   sum if `renormalize` is 1; the softmax over just the chosen s if it is 2), times `weight_scale`.
 // Shared memory per warp: s[experts], candidates[experts], group score[group_count], and the token's row in 32-bit where it is staged.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, int* __restrict__ chosen, float* __restrict__ weights,
                                  int tokens, int width, int experts, int top, int group_count, int group_keep, int score_kind, int renormalize,
-                                 float weight_scale, int row_floats, int group_floats) {
+                                 float weight_scale, int row_floats, int group_floats, const float* __restrict__ bias) {
     extern __shared__ __align__(16) float shared[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int token = blockIdx.x * warps + warp;
@@ -74,7 +74,13 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         }
     }
     __syncwarp();
-    if (score_kind == 1) {
+    if (bias != nullptr) {
+        for (int e = lane; e < experts; e += 32) scores[e] += bias[e];
+        __syncwarp();
+    }
+    if (score_kind == 2) {
+        // the logits themselves rank the experts
+    } else if (score_kind == 1) {
         float largest = -INFINITY;
         for (int e = lane; e < experts; e += 32) largest = fmaxf(largest, scores[e]);
         largest = warp_max(largest);
@@ -139,7 +145,17 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
         }
         __syncwarp();
     }
-    if (lane == 0) {
+    if (lane == 0 && renormalize == 2) {
+        // the softmax over the chosen scores only (the first chosen is the largest)
+        float* mine = weights + static_cast<size_t>(token) * top;
+        const float largest = mine[0];
+        float sum = 0.0f;
+        for (int round = 0; round < top; ++round) {
+            mine[round] = expf(mine[round] - largest);
+            sum += mine[round];
+        }
+        for (int round = 0; round < top; ++round) mine[round] = mine[round] / sum * weight_scale;
+    } else if (lane == 0) {
         const float factor = (renormalize && total > 0.0f ? 1.0f / total : 1.0f) * weight_scale;
         if (factor != 1.0f)
             for (int round = 0; round < top; ++round) weights[static_cast<size_t>(token) * top + round] *= factor;
@@ -152,13 +168,20 @@ __device__ __forceinline__ float moe_activate(float v, int activation) {
     return v;
 }
 
+// The hidden value of a gated expert from its two 32-bit sums, as a value of T.
+template <typename T>
+__device__ __forceinline__ float moe_hidden(float gate, float up, int activation, float limit) {
+    if (activation == kSigmoidLimit) return round_to<T>(sigmoid_limit_gate(gate, up, limit));
+    return round_to<T>(round_to<T>(moe_activate(round_to<T>(gate), activation)) * round_to<T>(up));
+}
+
 // One block per (token, chosen expert) pair p: hidden = act(W_gate[e] x) * (W_up[e] x), rounded to T; out[p] = W_down[e] hidden
 // in 32-bit.  A warp per output row, lanes along the row, sums in lane order then over the warp.
 //   gate, up [experts, ff, width];  down [experts, width, ff];  out [pairs, width] (32-bit)
 template <typename T>
 __global__ void moe_expert_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ up, const T* __restrict__ down,
                                          const int* __restrict__ chosen, float* __restrict__ out, int top, int width, int ff, int experts,
-                                         int activation) {
+                                         int activation, float limit) {
     extern __shared__ float shared[];
     float* x_s = shared;           // width
     float* hidden = shared + width;   // ff
@@ -185,7 +208,7 @@ __global__ void moe_expert_stream_kernel(const T* __restrict__ x, const T* __res
         }
         g = warp_sum(g);
         u = warp_sum(u);
-        if (lane == 0) hidden[f] = round_to<T>(round_to<T>(moe_activate(round_to<T>(g), activation)) * round_to<T>(u));
+        if (lane == 0) hidden[f] = moe_hidden<T>(g, u, activation, limit);
     }
     __syncthreads();
     const T* down_rows = down + static_cast<size_t>(expert) * width * ff;
@@ -263,7 +286,7 @@ __device__ __forceinline__ void four_dots(const float* __restrict__ x_s, const T
 template <typename T>
 __global__ void __launch_bounds__(32 * kStreamWarps)
 moe_gate_up_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ up, const int* __restrict__ chosen,
-                          T* __restrict__ hidden, int top, int width, int ff, int experts, int activation) {
+                          T* __restrict__ hidden, int top, int width, int ff, int experts, int activation, float limit) {
     extern __shared__ float x_s[];   // width
     const int pair = blockIdx.x, token = pair / top, expert = chosen[pair];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -291,7 +314,7 @@ moe_gate_up_stream_kernel(const T* __restrict__ x, const T* __restrict__ gate, c
         if (lane < 4 && f0 + lane < ff) {
             const float gv = lane == 0 ? g[0] : lane == 1 ? g[1] : lane == 2 ? g[2] : g[3];
             const float uv = lane == 0 ? u[0] : lane == 1 ? u[1] : lane == 2 ? u[2] : u[3];
-            hidden[static_cast<size_t>(pair) * ff + f0 + lane] = from_float<T>(round_to<T>(moe_activate(round_to<T>(gv), activation)) * round_to<T>(uv));
+            hidden[static_cast<size_t>(pair) * ff + f0 + lane] = from_float<T>(moe_hidden<T>(gv, uv, activation, limit));
         }
     }
 }
@@ -379,7 +402,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16* __restrict__ b_first, const __nv_bfloat16* __restrict__ b_second,
                    const int* __restrict__ offsets, const int* __restrict__ sorted, __nv_bfloat16* __restrict__ hidden_out, float* __restrict__ pair_out,
-                   int experts, int top, int n_total, int k_total, int activation) {
+                   int experts, int top, int n_total, int k_total, int activation, float limit) {
     __shared__ __align__(16) __nv_bfloat16 a_s[2][kGroupedM][kGroupedPitch];
     __shared__ __align__(16) __nv_bfloat16 b_s[GATED ? 2 : 1][2][kGroupedN][kGroupedPitch];
     __shared__ int row_source[kGroupedM];   // GATED: the token of the row's pair; else: the pair itself; -1 past the expert's pairs
@@ -477,8 +500,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
                 if constexpr (GATED) {
                     using T = __nv_bfloat16;
                     const float gate_value = acc[0][j][2 * half + e], up_value = acc[1][j][2 * half + e];
-                    hidden_out[static_cast<size_t>(first + row) * n_total + n] =
-                        from_float<T>(round_to<T>(moe_activate(round_to<T>(gate_value), activation)) * round_to<T>(up_value));
+                    hidden_out[static_cast<size_t>(first + row) * n_total + n] = from_float<T>(moe_hidden<T>(gate_value, up_value, activation, limit));
                 } else {
                     pair_out[static_cast<size_t>(row_source[row]) * n_total + n] = acc[0][j][2 * half + e];
                 }
@@ -492,7 +514,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ a_base, const __nv_bfloat16
 extern "C" {
 
 int lb_moe_route(const void* x, const float* router, int* chosen, float* weights, int tokens, int width, int experts, int top, int group_count,
-                 int group_keep, int score_kind, int renormalize, float weight_scale, int dtype, cudaStream_t stream) {
+                 int group_keep, int score_kind, int renormalize, float weight_scale, int dtype, cudaStream_t stream, const float* bias) {
     if (tokens == 0) return 0;
     if (experts < 1 || top < 1 || top > experts || group_count < 1 || experts % group_count != 0 || group_keep < 1 || group_keep > group_count) return -2;
     constexpr int kWarps = 4;
@@ -508,13 +530,13 @@ int lb_moe_route(const void* x, const float* router, int* chosen, float* weights
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         kernel<<<(tokens + kWarps - 1) / kWarps, 32 * kWarps, shared, stream>>>(
             static_cast<const T*>(x), router, chosen, weights, tokens, width, experts, top, group_count, group_keep, score_kind, renormalize, weight_scale,
-            row_floats, padded_groups);
+            row_floats, padded_groups, bias);
     })
     return LB_LAUNCH_RESULT();
 }
 
 int lb_moe_expert_stream(const void* x, const void* gate, const void* up, const void* down, const int* chosen, float* out, int pairs, int top,
-                         int width, int ff, int experts, int activation, int dtype, cudaStream_t stream) {
+                         int width, int ff, int experts, int activation, int dtype, cudaStream_t stream, float limit) {
     if (pairs == 0) return 0;
     const size_t shared = (static_cast<size_t>(width) + ff) * sizeof(float);
     if (shared > 200 * 1024) return -2;
@@ -522,7 +544,7 @@ int lb_moe_expert_stream(const void* x, const void* gate, const void* up, const 
         auto kernel = lb::moe_expert_stream_kernel<T>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         kernel<<<pairs, 256, shared, stream>>>(static_cast<const T*>(x), static_cast<const T*>(gate), static_cast<const T*>(up), static_cast<const T*>(down),
-                                               chosen, out, top, width, ff, experts, activation);
+                                               chosen, out, top, width, ff, experts, activation, limit);
     })
     return LB_LAUNCH_RESULT();
 }
@@ -539,7 +561,7 @@ int lb_moe_combine(const float* expert_out, const float* weights, const int* cho
 // The two products of the few-token path: `hidden` [pairs, ff] in the activation type, `out` [pairs, width] in 32-bit.
 // Rows of 16-byte multiples only (width and ff multiples of 8 for bfloat16, of 4 for float32): -2 otherwise.
 int lb_moe_expert_stream_wide(const void* x, const void* gate, const void* up, const void* down, const int* chosen, void* hidden, float* out, int pairs,
-                              int top, int width, int ff, int experts, int activation, int dtype, cudaStream_t stream) {
+                              int top, int width, int ff, int experts, int activation, int dtype, cudaStream_t stream, float limit) {
     if (pairs == 0) return 0;
     const int vector = dtype == lb::kBFloat16 ? 8 : 4;
     if (width % vector != 0 || ff % vector != 0 || width * sizeof(float) > 160 * 1024 || ff * sizeof(float) > 160 * 1024) return -2;
@@ -550,7 +572,7 @@ int lb_moe_expert_stream_wide(const void* x, const void* gate, const void* up, c
         if (width * sizeof(float) > 48 * 1024) cudaFuncSetAttribute(first, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(width * sizeof(float)));
         if (ff * sizeof(float) > 48 * 1024) cudaFuncSetAttribute(second, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ff * sizeof(float)));
         first<<<up_grid, 32 * lb::kStreamWarps, width * sizeof(float), stream>>>(static_cast<const T*>(x), static_cast<const T*>(gate), static_cast<const T*>(up), chosen,
-                                                                                static_cast<T*>(hidden), top, width, ff, experts, activation);
+                                                                                static_cast<T*>(hidden), top, width, ff, experts, activation, limit);
         second<<<down_grid, 32 * lb::kStreamWarps, ff * sizeof(float), stream>>>(static_cast<const T*>(hidden), static_cast<const T*>(down), chosen, out, width, ff, experts);
     })
     return LB_LAUNCH_RESULT();
@@ -560,7 +582,7 @@ int lb_moe_expert_stream_wide(const void* x, const void* gate, const void* up, c
 // `offsets` [experts + 1] and `sorted` [pairs], then the two grouped products.  `hidden` is [pairs, ff] (rows in sorted
 // order), `out` [pairs, width] in 32-bit (rows in pair order; rows of pairs without an expert are not written).
 int lb_moe_experts_grouped(const void* x, const void* gate, const void* up, const void* down, const int* chosen, int* offsets, int* sorted, void* hidden,
-                           float* out, int pairs, int top, int width, int ff, int experts, int activation, cudaStream_t stream) {
+                           float* out, int pairs, int top, int width, int ff, int experts, int activation, cudaStream_t stream, float limit) {
     if (pairs == 0) return 0;
     if (width % 8 != 0 || ff % 8 != 0 || experts < 1 || experts > 1024) return -2;
     lb::moe_sort_kernel<<<1, 1024, 2 * experts * sizeof(int), stream>>>(chosen, pairs, experts, offsets, sorted);
@@ -568,9 +590,9 @@ int lb_moe_experts_grouped(const void* x, const void* gate, const void* up, cons
     const auto* x16 = static_cast<const __nv_bfloat16*>(x);
     lb::moe_grouped_kernel<true><<<dim3(tiles, (ff + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
         x16, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(up), offsets, sorted, static_cast<__nv_bfloat16*>(hidden), nullptr, experts,
-        top, ff, width, activation);
+        top, ff, width, activation, limit);
     lb::moe_grouped_kernel<false><<<dim3(tiles, (width + lb::kGroupedN - 1) / lb::kGroupedN), 128, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(down), nullptr, offsets, sorted, nullptr, out, experts, top, width, ff, activation);
+        static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(down), nullptr, offsets, sorted, nullptr, out, experts, top, width, ff, activation, limit);
     return LB_LAUNCH_RESULT();
 }
 

@@ -68,7 +68,7 @@ class ScaledSum:
         return total.to(self.terms[0][0].dtype)
 
 
-_ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2}
+_ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2, "sigmoid_limit": 3}  # the last takes a `limit`, see csrc/common.cuh
 _launches = 0
 
 
@@ -140,8 +140,8 @@ def _lib() -> ctypes.CDLL:
 
 
 # --------------------------------------------------------------------------- elementwise
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor) -> None:
-    """``out[t] = float(table[ids[t]]) * scale`` into the 32-bit residual stream."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor, accumulate: bool = False) -> None:
+    """``out[t] = float(table[ids[t]]) * scale`` into the 32-bit residual stream (``accumulate``: added to it)."""
     _check(table, "table")
     _check(ids, "ids", torch.int32)
     _check(out, "out", torch.float32)
@@ -150,7 +150,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: floa
     if table.shape[1] != dim or ids.numel() < tokens:
         raise KernelError("embed: shapes of table, ids and out do not agree")
     code = _lib().lb_embed(_ptr(table), _ptr(ids), _ptr(out), c_int(tokens), c_int(dim), c_int(vocab), c_float(scale),
-                           c_int(dtype_code(table.dtype)), _ptr(status), _stream())
+                           c_int(dtype_code(table.dtype)), _ptr(status), _stream(), c_int(1 if accumulate else 0))
     _done(code, "embed")
 
 
@@ -164,8 +164,10 @@ def rmsnorm(
     rows: torch.Tensor | None = None,
     scale_offset: float = 0.0,
     write_back: bool = False,
+    exact: bool = False,
 ) -> None:
     """``out[r] = rms_norm(x[src] + delta[src]) * (weight + offset)``, ``src = rows[r]`` or ``r``.
+    ``exact``: 32-bit throughout and rounded once (otherwise the normalised value and the scale are each rounded first).
 
     ``x`` is the 32-bit residual stream or has ``out``'s type.  With ``write_back`` the sum is
     stored back into ``x``.  ``delta`` may be a :class:`SlicedSum`: its slices are added here.
@@ -200,7 +202,7 @@ def rmsnorm(
         raise KernelError(f"rmsnorm: rows of {dim} elements exceed the supported 50000")
     code = _lib().lb_rmsnorm(_ptr(x), c_int(1 if x.dtype == torch.float32 else 0),
                              _ptr(delta), _ptr(partials), c_int(slices), c_longlong(slice_stride), _ptr(weight), _ptr(rows), _ptr(out), c_int(out_rows), c_int(dim), c_float(eps),
-                             c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream())
+                             c_float(scale_offset), c_int(1 if write_back else 0), c_int(dtype_code(out.dtype)), _stream(), c_int(1 if exact else 0))
     _done(code, "rmsnorm")
 
 
@@ -249,10 +251,11 @@ def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
 
 
 def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", weight: torch.Tensor, eps: float, *,
-                    scale_offset: float = 0.0, rounded: torch.Tensor | None = None) -> None:
+                    scale_offset: float = 0.0, rounded: torch.Tensor | None = None, next_norm: tuple | None = None) -> None:
     """``residual += rms_norm(delta) * (weight + offset)`` on the 32-bit residual stream, everything in 32-bit;
     ``delta`` may be a :class:`ScaledSum` of one or two terms, summed here.  ``rounded`` (optional, of
-    ``delta``'s type) receives the new stream rounded to that type."""
+    ``delta``'s type) receives the new stream rounded to that type or, with ``next_norm = (weight, eps, offset)``,
+    the RMS norm of the new stream under that weight (32-bit, rounded once): what the next sublayer begins with."""
     _check(residual, "residual", torch.float32)
     _check(weight, "weight", torch.float32)
     terms = delta.terms if isinstance(delta, ScaledSum) else [(delta, 1.0, None)]
@@ -274,10 +277,21 @@ def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", w
         if rounded.shape != residual.shape:
             raise KernelError("norm_accumulate: rounded and the residual stream differ in shape")
     second = terms[1] if len(terms) == 2 else (None, 0.0, None)
+    next_weight, next_eps, next_offset = next_norm if next_norm is not None else (None, 0.0, 0.0)
+    if next_weight is not None:
+        _check(next_weight, "next_norm weight", torch.float32)
+        if rounded is None or next_weight.numel() != residual.shape[1]:
+            raise KernelError("norm_accumulate: the next norm needs `rounded` and a weight of one element per column")
     code = _lib().lb_norm_accumulate(_ptr(residual), _ptr(first), _ptr(terms[0][2]), c_float(terms[0][1]), _ptr(second[0]), _ptr(second[2]), c_float(second[1]),
                                      _ptr(weight), _ptr(rounded), c_int(residual.shape[0]), c_int(residual.shape[1]), c_float(eps), c_float(scale_offset),
-                                     c_int(dtype_code(first.dtype)), _stream())
+                                     c_int(dtype_code(first.dtype)), _stream(), _ptr(next_weight), c_float(next_eps), c_float(next_offset))
     _done(code, "norm_accumulate")
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """``x *= factor`` in place on a 32-bit tensor."""
+    _check(x, "x", torch.float32)
+    _done(_lib().lb_scale(_ptr(x), c_float(factor), c_longlong(x.numel()), _stream()), "scale")
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -319,8 +333,9 @@ def feed_tokens(token_ids: torch.Tensor, segment_start: torch.Tensor, segment_le
     _done(code, "feed_tokens")
 
 
-def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """``out = up * act(gate)`` for ``fused = [up ; gate]`` along the last dimension."""
+def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0) -> None:
+    """``out = up * act(gate)`` for ``fused = [up ; gate]`` along the last dimension (``"sigmoid_limit"``:
+    ``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``)."""
     _check(fused, "fused")
     _check(out, "out", fused.dtype)
     if activation not in _ACTIVATIONS:
@@ -329,7 +344,7 @@ def gated_activation(fused: torch.Tensor, out: torch.Tensor, activation: str) ->
     if fused.shape != (tokens, 2 * hidden):
         raise KernelError("gated_activation: fused must be [tokens, 2 * hidden]")
     code = _lib().lb_gated_activation(_ptr(fused), _ptr(out), c_int(tokens), c_int(hidden), c_int(_ACTIVATIONS[activation]),
-                                      c_int(dtype_code(out.dtype)), _stream())
+                                      c_int(dtype_code(out.dtype)), _stream(), c_float(limit))
     _done(code, "gated_activation")
 
 
@@ -845,19 +860,115 @@ def gated_delta_rule(
     return out
 
 
+# ---------------------------------------------------------------------- latent attention
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, transpose_weight: bool = False) -> torch.Tensor:
+    """One small product per head: ``out[h] = x[h] @ weight[h]`` (``transpose_weight``: ``x[h] @ weight[h].T``) for
+    ``x [heads, tokens, k]`` (any strides with the last one 1) and ``weight [heads, k, n]`` (``[heads, n, k]``);
+    32-bit accumulation, ``out [heads, tokens, n]`` contiguous in ``x``'s type.  A library product (batched)."""
+    if x.dim() != 3 or weight.dim() != 3 or x.shape[0] != weight.shape[0] or x.dtype != weight.dtype or not x.is_cuda:
+        raise KernelError("heads_linear: x [heads, tokens, k] and weight [heads, ., .] must agree in heads, type and device")
+    return torch.bmm(x, weight.transpose(1, 2) if transpose_weight else weight)
+
+
+def _check_latent_pages(pages: torch.Tensor, block_table: torch.Tensor, latent: int, rope: int) -> tuple[int, int, int]:
+    _check(pages, "pages")
+    _check(block_table, "block_table", torch.int32)
+    if pages.dim() != 4 or pages.shape[2:] != (1, latent + rope):
+        raise KernelError("the latent cache must be [pages, page_size, 1, latent + rope]")
+    if block_table.dim() != 2:
+        raise KernelError("block_table must be [segments, max_blocks]")
+    return pages.shape[1], pages.shape[0], block_table.shape[1]
+
+
+def latent_prepare(q: torch.Tensor, q_latent: torch.Tensor, down: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *, norm_weight: torch.Tensor,
+                   eps: float, scale_offset: float, inv_freq: torch.Tensor, positions: torch.Tensor, token_segment: torch.Tensor,
+                   block_table: torch.Tensor, num_heads: int, head_dim: int, latent: int, rope: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Latent attention's step between the projections and the attention.  ``q [tokens, heads * (head_dim + rope)]`` and
+    ``down [tokens, latent + rope]`` may be column slices of a wider product (row strides are passed on).  Writes the
+    row ``[norm(down[:latent]) * (norm_weight + scale_offset) | rope(down[latent:])]`` into the token's page and the
+    queries ``[q_latent[h, t] | rope(q[t, h, head_dim:])]`` into ``q_out [tokens, heads, latent + rope]``; the rotation
+    pairs channel ``i`` with ``i + rope / 2``."""
+    tokens = q_out.shape[0]
+    for name, tensor in (("q", q), ("down", down)):
+        if not tensor.is_cuda or tensor.dim() != 2 or tensor.stride(1) != 1 or tensor.dtype != q_out.dtype or tensor.shape[0] != tokens:
+            raise KernelError(f"latent_prepare: {name} must be a [tokens, .] CUDA tensor of q_out's type with unit column stride")
+    _check(q_latent, "q_latent", q_out.dtype)
+    _check(q_out, "q_out")
+    _check(norm_weight, "norm_weight", torch.float32)
+    _check(inv_freq, "inv_freq", torch.float32)
+    _check(positions, "positions", torch.int32)
+    _check(token_segment, "token_segment", torch.int32)
+    if (q.shape[1] != num_heads * (head_dim + rope) or down.shape[1] != latent + rope or q_latent.shape != (num_heads, tokens, latent)
+            or q_out.shape != (tokens, num_heads, latent + rope) or norm_weight.numel() != latent or inv_freq.numel() != rope // 2 or rope % 2):
+        raise KernelError("latent_prepare: the sizes of q, q_latent, down, q_out, the norm's weight and the frequencies do not agree")
+    page_size, num_pages, max_blocks = _check_latent_pages(pages, block_table, latent, rope)
+    if pages.dtype != q_out.dtype:
+        raise KernelError("latent_prepare: cache and activations differ in type")
+    code = _lib().lb_latent_prepare(_ptr(q), c_int(q.stride(0)), _ptr(q_latent), _ptr(down), c_int(down.stride(0)), _ptr(q_out), _ptr(pages), _ptr(norm_weight),
+                                    c_float(eps), c_float(scale_offset), _ptr(inv_freq), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens),
+                                    c_int(num_heads), c_int(head_dim), c_int(latent), c_int(rope), c_int(page_size), c_int(num_pages), c_int(max_blocks),
+                                    c_int(1 if write_kv else 0), c_int(dtype_code(q_out.dtype)), _ptr(status), _stream())
+    _done(code, "latent_prepare")
+
+
+def latent_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *, positions: torch.Tensor, token_segment: torch.Tensor,
+                           block_table: torch.Tensor, num_heads: int, latent: int, rope: int, scale: float, window: int | None,
+                           status: torch.Tensor) -> None:
+    """Causal (optionally windowed) attention of queries ``[tokens, heads, latent + rope]`` over their requests' cached rows
+    ``[latent | rope]``: ``out[t, h] = sum_j softmax_j(q[t, h] . row_j * scale) row_j[:latent]``, all in 32-bit."""
+    _check(q, "q")
+    _check(out, "out", q.dtype)
+    tokens = q.shape[0]
+    if q.shape != (tokens, num_heads, latent + rope) or out.shape != (tokens, num_heads, latent):
+        raise KernelError("latent_attention: q must be [tokens, heads, latent + rope] and out [tokens, heads, latent]")
+    page_size, num_pages, max_blocks = _check_latent_pages(pages, block_table, latent, rope)
+    if pages.dtype != q.dtype:
+        raise KernelError("latent_attention: cache and queries differ in type")
+    if latent > 1024 or (latent + rope) * 4 > 40 * 1024:
+        raise KernelError(f"latent_attention: latent {latent} + rope {rope} exceed what the kernel supports")
+    code = _lib().lb_latent_attention_plain(_ptr(q), _ptr(pages), _ptr(out), _ptr(positions), _ptr(token_segment), _ptr(block_table), c_int(tokens),
+                                            c_int(num_heads), c_int(latent), c_int(rope), c_int(page_size), c_int(num_pages), c_int(max_blocks),
+                                            c_float(scale), c_int(window if window else 0), c_int(dtype_code(q.dtype)), _ptr(status), _stream())
+    _done(code, "latent_attention_plain")
+
+
+def gate_heads(values: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> None:
+    """``out[t, h * vdim + j] = values[h, t, j] * sigmoid(gate[t, h * vdim + j])`` (``gate=None``: no gate); ``gate`` may
+    be a column slice of a wider product."""
+    _check(values, "values")
+    _check(out, "out", values.dtype)
+    heads, tokens, value_dim = values.shape
+    if out.shape != (tokens, heads * value_dim):
+        raise KernelError("gate_heads: out must be [tokens, heads * vdim]")
+    stride = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != values.dtype or gate.shape != out.shape or gate.stride(1) != 1:
+            raise KernelError("gate_heads: gate must be [tokens, heads * vdim] of the values' type with unit column stride")
+        stride = gate.stride(0)
+    code = _lib().lb_gate_heads(_ptr(values), _ptr(gate), c_int(stride), _ptr(out), c_int(tokens), c_int(heads), c_int(value_dim),
+                                c_int(dtype_code(values.dtype)), _stream())
+    _done(code, "gate_heads")
+
+
 # ------------------------------------------------------------------------ routed experts
-_ROUTER_SCORES = {"sigmoid": 0, "softmax": 1}
+_ROUTER_SCORES = {"sigmoid": 0, "softmax": 1, "logits": 2}
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: int = 1, group_keep: int = 1, score: str = "sigmoid",
-              renormalize: bool = False, weight_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+              renormalize: bool = False, weight_scale: float = 1.0, bias: torch.Tensor | None = None,
+              chosen_softmax: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Chooses ``top`` experts per token: 32-bit router logits ``x @ router.T``, scores (``"sigmoid"`` or
     ``"softmax"``), only experts of the ``group_keep`` best of ``group_count`` groups of neighbours eligible
     (a group's score: the sum of its two largest scores).  Returns ``(chosen int32 [tokens, top], weights
-    float32 [tokens, top])``, the weights being the chosen scores (over their sum if ``renormalize``) times
-    ``weight_scale``."""
+    float32 [tokens, top])``, the weights being the chosen scores (over their sum if ``renormalize``; their softmax
+    if ``chosen_softmax``) times ``weight_scale``.  ``bias`` (32-bit, one per expert) is added to the logits;
+    ``score="logits"`` ranks by the logits themselves."""
     _check(x, "x")
     _check(router, "router", torch.float32)
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != router.shape[0]:
+            raise KernelError("moe_route: the bias must have one element per expert")
     if score not in _ROUTER_SCORES:
         raise KernelError(f"moe_route: unknown score {score!r}; known: {sorted(_ROUTER_SCORES)}")
     tokens, width = x.shape
@@ -871,8 +982,8 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: i
     chosen = torch.empty(tokens, top, dtype=torch.int32, device=x.device)
     weights = torch.empty(tokens, top, dtype=torch.float32, device=x.device)
     code = _lib().lb_moe_route(_ptr(x), _ptr(router), _ptr(chosen), _ptr(weights), c_int(tokens), c_int(width), c_int(experts), c_int(top), c_int(group_count),
-                               c_int(group_keep), c_int(_ROUTER_SCORES[score]), c_int(1 if renormalize else 0), c_float(weight_scale),
-                               c_int(dtype_code(x.dtype)), _stream())
+                               c_int(group_keep), c_int(_ROUTER_SCORES[score]), c_int(2 if chosen_softmax else 1 if renormalize else 0), c_float(weight_scale),
+                               c_int(dtype_code(x.dtype)), _stream(), _ptr(bias))
     _done(code, "moe_route")
     return chosen, weights
 
@@ -881,7 +992,7 @@ MOE_STREAM_MAX_PAIRS = 16  # up to this many (token, expert) pairs each pair str
 
 
 def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
-                activation: str = "silu", path: str | None = None) -> torch.Tensor:
+                activation: str = "silu", path: str | None = None, limit: float = 0.0) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * down[e] (act(gate[e] x[t]) * (up[e] x[t]))`` with ``e = chosen[t, k]``;
     ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  The weighted sum is
     32-bit, in the order of ``k``; a pair whose expert is no expert counts nothing.  ``path`` forces one of the
@@ -916,7 +1027,7 @@ def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
         order = torch.empty(pairs, dtype=torch.int32, device=x.device)
         hidden = torch.empty(pairs, ff, dtype=x.dtype, device=x.device)
         code = lib.lb_moe_experts_grouped(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(offsets), _ptr(order), _ptr(hidden), _ptr(pair_out),
-                                          c_int(pairs), c_int(top), c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), _stream())
+                                          c_int(pairs), c_int(top), c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), _stream(), c_float(limit))
         _done(code, "moe_experts_grouped", 3)
     elif path == "stream":
         # few pairs: each streams its expert's rows, 16 bytes a lane, the rows shared out over many blocks
@@ -924,11 +1035,11 @@ def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
             raise KernelError("moe_experts: the streaming kernels take rows of 16-byte multiples")
         hidden = torch.empty(pairs, ff, dtype=x.dtype, device=x.device)
         code = lib.lb_moe_expert_stream_wide(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(hidden), _ptr(pair_out), c_int(pairs), c_int(top),
-                                             c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
+                                             c_int(width), c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream(), c_float(limit))
         _done(code, "moe_expert_stream_wide", 2)
     elif path == "plain":
         code = lib.lb_moe_expert_stream(_ptr(x), _ptr(gate), _ptr(up), _ptr(down), _ptr(chosen), _ptr(pair_out), c_int(pairs), c_int(top), c_int(width),
-                                        c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream())
+                                        c_int(ff), c_int(experts), c_int(_ACTIVATIONS[activation]), c_int(dtype_code(x.dtype)), _stream(), c_float(limit))
         _done(code, "moe_expert_stream")
     else:
         raise KernelError(f"moe_experts: unknown path {path!r}")
@@ -1018,7 +1129,7 @@ def skinny_supported(x: torch.Tensor, rows: int) -> bool:
 
 
 def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, epilogue: str, activation: str = "identity", conv: dict | None = None,
-            prefetch: bool = True) -> None:
+            prefetch: bool = True, limit: float = 0.0) -> None:
     """``prefetch``: the kernel asks for its weights towards L2 before it waits for the kernel before it; off where
     that kernel does not let it start early (see :func:`successor_starts_early`)."""
     conv = conv or {}
@@ -1026,7 +1137,7 @@ def _skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n: int, ep
         _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(x.shape[1]), c_int(n), c_int(_SKINNY_EPILOGUES[epilogue]),
         c_int(_ACTIVATIONS[activation]), _ptr(conv.get("state")), _ptr(conv.get("weight")), _ptr(conv.get("bias")), _ptr(conv.get("token_segment")),
         _ptr(conv.get("segment_start")), _ptr(conv.get("segment_length")), _ptr(conv.get("segment_slot")), c_int(conv.get("segments", 0)),
-        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), c_int(1 if prefetch else 0), _ptr(conv.get("status")), _stream())
+        c_int(conv.get("taps", 0)), c_int(conv.get("num_slots", 0)), c_int(1 if prefetch else 0), _ptr(conv.get("status")), _stream(), c_float(limit))
     _done(code, f"gemm_skinny[{epilogue}]")
 
 
@@ -1194,8 +1305,9 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, residual: torch.Ten
     return torch.mm(x, weight.t())
 
 
-def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str, status: torch.Tensor | None = None) -> torch.Tensor:
-    """``up * act(gate)`` for ``[up ; gate] = x @ up_gate.T`` (``up_gate``: ``[2 * hidden, width]``)."""
+def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str, status: torch.Tensor | None = None, limit: float = 0.0) -> torch.Tensor:
+    """``up * act(gate)`` for ``[up ; gate] = x @ up_gate.T`` (``up_gate``: ``[2 * hidden, width]``); ``limit``: of the
+    ``"sigmoid_limit"`` activation."""
     _check(x, "x")
     _check(up_gate, "up_gate", x.dtype)
     if activation not in _ACTIVATIONS:
@@ -1203,15 +1315,17 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str, status
     hidden = up_gate.shape[0] // 2
     if x.shape[-1] != up_gate.shape[1] or up_gate.shape[0] != 2 * hidden:
         raise KernelError("gated_linear: shapes of x and up_gate do not agree")
-    if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
+    fused_on_tcgen05 = activation != "sigmoid_limit"   # the tcgen05 product's gated epilogue has the one-input activations only
+    if fused_on_tcgen05 and USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
         return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
     out = torch.empty(x.shape[0], hidden, dtype=x.dtype, device=x.device)
     if skinny_supported(x, hidden):
-        _skinny(x, up_gate, out, hidden, "gated", activation)
+        _skinny(x, up_gate, out, hidden, "gated", activation, limit=limit)
         return out
-    if USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
+    if fused_on_tcgen05 and USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
         return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
-    gated_activation(linear(x, up_gate, status=status), out, activation)
+    fused = linear(x, up_gate, status=status)
+    gated_activation(fused.sum() if isinstance(fused, SlicedSum) else fused, out, activation, limit)
     return out
 
 

@@ -52,6 +52,18 @@ def shared_tile_keys(num_tiles: int, num_heads: int, num_groups: int, sms: int, 
     return 0
 
 
+def _interleaved_to_half(head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """The order of a head's channels that turns pairs (2i, 2i + 1) of its first ``rotary_dim`` channels into pairs
+    (i, i + rotary_dim / 2): the even ones, the odd ones, then the channels that are not rotated."""
+    return torch.cat([torch.arange(0, rotary_dim, 2), torch.arange(1, rotary_dim, 2), torch.arange(rotary_dim, head_dim)])
+
+
+def _reorder_heads(rows: torch.Tensor, heads: int, order: torch.Tensor) -> torch.Tensor:
+    """``rows`` ([heads * head_dim, ...]) with every head's rows taken in ``order``."""
+    per_head = rows.reshape(heads, order.numel(), *rows.shape[1:])
+    return per_head[:, order].reshape(rows.shape).contiguous()
+
+
 @register_part(AttentionSpec)
 class Attention(Mixer):
     graph_safe = True
@@ -65,11 +77,25 @@ class Attention(Mixer):
             raise ValueError(f"keep_first must not be negative, got {spec.keep_first}")
         self.value_dim = spec.value_dim or spec.head_dim
         self.keep_first = spec.keep_first if spec.window is not None else 0
-        self.qkv = runtime.matrix(torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0))
+        q_proj, k_proj = tensors["q_proj"], tensors["k_proj"]
+        q_bias, k_bias = (tensors["q_bias"], tensors["k_bias"]) if spec.has_bias else (None, None)
+        if isinstance(spec.position, RopeSpec) and spec.position.pairing == "interleaved":
+            # The kernels rotate channel i with i + rotary_dim / 2.  Scores are sums over a head's channels, so the same
+            # reordering of the channels of q and k changes none of them: the even channels of the rotated part first,
+            # then the odd ones, and pair (2i, 2i + 1) becomes pair (i, i + rotary_dim / 2) with its angle.
+            if spec.qk_norm is not None:
+                raise ValueError("interleaved rotation with a per-head norm is not supported (the norm's weight would have to be reordered too)")
+            order = _interleaved_to_half(spec.head_dim, spec.position.rotary_dim)
+            q_proj, k_proj = _reorder_heads(q_proj, spec.num_heads, order), _reorder_heads(k_proj, spec.num_groups, order)
+            if spec.has_bias:
+                q_bias, k_bias = _reorder_heads(q_bias, spec.num_heads, order), _reorder_heads(k_bias, spec.num_groups, order)
+        elif isinstance(spec.position, RopeSpec) and spec.position.pairing != "half":
+            raise ValueError(f"unknown rotary pairing {spec.position.pairing!r}; known: 'half', 'interleaved'")
+        self.qkv = runtime.matrix(torch.cat([q_proj, k_proj, tensors["v_proj"]], dim=0))
         self.out_proj = runtime.matrix(tensors["out_proj"])
         # Biases are 32-bit vectors: those of q, k and v are added where the product's rows are split into heads,
         # the output's by whoever consumes the output (`output_bias`), or here.
-        self.qkv_bias = runtime.vector(torch.cat([tensors["q_bias"], tensors["k_bias"], tensors["v_bias"]], dim=0)) if spec.has_bias else None
+        self.qkv_bias = runtime.vector(torch.cat([q_bias, k_bias, tensors["v_bias"]], dim=0)) if spec.has_bias else None
         self.output_bias = runtime.vector(tensors["out_bias"]) if spec.has_bias else None
         self.q_norm = self.k_norm = None
         self.norm_eps, self.norm_offset = 0.0, 0.0

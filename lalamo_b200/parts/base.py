@@ -103,6 +103,7 @@ class PagedKVNeed(CacheNeed):
     window: int | None = None
     value_dim: int | None = None  # size of a value head; None: head_dim
     keep_first: int = 0  # under a window: the first positions of a request that are kept all the same
+    values_in_keys: bool = False  # True: a row holds all a token leaves behind (values are read from the key rows); no value pages
 
 
 @dataclass(frozen=True)
@@ -132,7 +133,7 @@ class CacheView:
 @dataclass
 class PagedKVView(CacheView):
     k_pages: torch.Tensor  # [pages, page_size, groups, head_dim]
-    v_pages: torch.Tensor  # [pages, groups, value_dim, page_size] (transposed)
+    v_pages: torch.Tensor | None  # [pages, groups, value_dim, page_size] (transposed); None where values are read from the key rows
     block_table: torch.Tensor  # int32 [segments, max_blocks], -1 where no page is held
 
 

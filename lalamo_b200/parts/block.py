@@ -21,7 +21,7 @@ import torch
 
 from .base import CacheView, FeedForward, Mixer, Norm, Part, Runtime, StepInputs, TensorDecl, build_part, part_type
 
-__all__ = ["Block", "OutputNormBlock", "PreNormBlock", "block_tensor_decls", "block_type", "build_block", "register_arrangement"]
+__all__ = ["Block", "OutputNormBlock", "PreNormBlock", "SandwichNormBlock", "block_tensor_decls", "block_type", "build_block", "register_arrangement"]
 
 _ARRANGEMENTS: dict[str, type["Block"]] = {}
 
@@ -158,6 +158,77 @@ class OutputNormBlock(Block):
         ops.residual_add(residual, norm.forward(delta))
         if rounded is not None:
             ops.cast_rows(residual, rounded)
+
+
+@register_arrangement("sandwich_norm")
+class SandwichNormBlock(Block):
+    """``x <- x + mixer_out_norm(mixer(mixer_norm(x))); x <- x + ffn_out_norm(ffn(ffn_norm(x)))``: a norm before and
+    after each sublayer, all of them 32-bit on the 32-bit stream.  The norm after a sublayer, the residual sum and the
+    norm before the next sublayer are one kernel (``RMSNorm.accumulate(..., then=...)``), also across blocks: the model
+    tells a block which norm the next block begins with (``step.carry["next_norm"]``), and the block leaves that norm
+    of its final stream in ``step.carry["normed_stream"]``."""
+
+    roles = ("mixer_norm", "mixer", "mixer_out_norm", "ffn_norm", "ffn", "ffn_out_norm")
+    mixer_norm: Norm
+    mixer_out_norm: Norm
+    ffn_norm: Norm | None
+    ffn: FeedForward | None
+    ffn_out_norm: Norm | None
+
+    def __init__(self, spec: Any, tensors: Mapping[tuple[str, str], torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        if (self.ffn is None) != (self.ffn_norm is None) or (self.ffn is None) != (self.ffn_out_norm is None):
+            raise ValueError("a sandwich block has a feed-forward with both of its norms, or none of the three")
+
+    @property
+    def first_norm(self) -> Norm:
+        """The norm this block begins with (a block before it may compute it on the way)."""
+        return self.mixer_norm
+
+    @staticmethod
+    def _fusable(norm: Norm | None) -> bool:
+        return norm is not None and getattr(norm.spec, "exact", False) and hasattr(norm, "accumulate")
+
+    def _add_normed(self, out_norm: Norm, residual: torch.Tensor, delta: "torch.Tensor", then: Norm | None) -> torch.Tensor | None:
+        """``residual += out_norm(delta)``; returns ``then(residual)`` if ``then`` is given."""
+        from .. import ops
+
+        if isinstance(delta, ops.SlicedSum):
+            delta = delta.sum()
+        if self._fusable(out_norm):
+            if then is not None and self._fusable(then) and then.spec.dim == out_norm.spec.dim:
+                normed = self.runtime.empty(*residual.shape)
+                out_norm.accumulate(residual, delta, normed, then=then)   # type: ignore[attr-defined]
+                return normed
+            out_norm.accumulate(residual, delta)   # type: ignore[attr-defined]
+        else:
+            if isinstance(delta, ops.ScaledSum):
+                delta = delta.sum()
+            ops.residual_add(residual, out_norm.forward(delta))
+        return then.forward(residual) if then is not None else None
+
+    def forward(self, residual: torch.Tensor, pending: torch.Tensor | None, step: StepInputs, cache: CacheView | None) -> torch.Tensor | None:
+        from .. import ops
+
+        following = step.carry.pop("next_norm", None)
+        carried = step.carry.pop("normed_stream", None)   # (the stream, the norm, that norm of the stream), left by the block before
+        if pending is not None:
+            ops.residual_add(residual, pending)
+            carried = None
+        if carried is not None and carried[0] is residual and carried[1] is self.mixer_norm:
+            normed = carried[2]
+        else:
+            normed = self.mixer_norm.forward(residual)
+        mixed = self.mixer.forward(normed, step, cache)
+        last_norm, last = self.mixer_out_norm, mixed
+        if self.ffn is not None:
+            normed = self._add_normed(self.mixer_out_norm, residual, mixed, self.ffn_norm)
+            last_norm, last = self.ffn_out_norm, self.ffn.forward(normed, step)
+        ahead = following if following is not None and self._fusable(following) and self._fusable(last_norm) else None
+        normed = self._add_normed(last_norm, residual, last, ahead)
+        if ahead is not None:
+            step.carry["normed_stream"] = (residual, ahead, normed)
+        return None
 
 
 def build_block(spec: Any, tensors: Mapping[tuple[str, str], torch.Tensor], runtime: Runtime) -> Block:

@@ -22,6 +22,10 @@ class Embedding(Part):
         """The residual stream ``[tokens, model_dim]`` in 32-bit for these token ids."""
         raise NotImplementedError
 
+    def add_to(self, residual: torch.Tensor, token_ids: torch.Tensor) -> None:
+        """``residual += forward(token_ids)``."""
+        ops.residual_add(residual, self.forward(token_ids, residual.shape[0]))
+
 
 class Head(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -44,6 +48,10 @@ class TokenEmbedding(Embedding):
         ops.embed(self.weight, token_ids, residual, self.spec.scale, self.runtime.status)
         return residual
 
+    def add_to(self, residual: torch.Tensor, token_ids: torch.Tensor) -> None:
+        """``residual += forward(token_ids)``: a model that feeds its input again further up gathers the rows again."""
+        ops.embed(self.weight, token_ids, residual, self.spec.scale, self.runtime.status, accumulate=True)
+
 
 @register_part(HeadSpec)
 class LMHead(Head):
@@ -58,4 +66,7 @@ class LMHead(Head):
         return {} if spec.tied else {"weight": TensorDecl((spec.vocab_size, spec.model_dim))}
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, out_dtype=torch.float32, status=self.runtime.status)
+        logits = ops.linear(x, self.weight, out_dtype=torch.float32, status=self.runtime.status)
+        if self.spec.scale != 1.0:
+            ops.scale_(logits, self.spec.scale)
+        return logits

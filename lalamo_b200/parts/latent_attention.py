@@ -1,0 +1,93 @@
+"""Latent attention over a paged cache: a token leaves one row ``[latent | rope]`` behind (its normed latent vector and
+one rotated key part shared by all heads), from which every head's keys and values are made.
+
+The heads' key and value projections are not applied to the cached rows.  A query head's unrotated part is taken into
+the latent's space instead (``W_uk_h^T q_h``), so that the score against a cached row is one dot product over
+``latent + rope`` channels; the attention sums the rows' latent parts, and the head's value projection is applied to
+that sum.  Both are exact rearrangements of ``(q . W_uk c)`` and ``sum_j p_j W_uv c_j``."""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .. import ops
+from ..config.plan import LatentAttentionSpec, RMSNormSpec, RopeSpec
+from .base import CacheNeed, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
+
+__all__ = ["LatentAttention"]
+
+
+@register_part(LatentAttentionSpec)
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec: LatentAttentionSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().__init__(spec, tensors, runtime)
+        if spec.window is not None and spec.window < 1:
+            raise ValueError(f"window must be positive, got {spec.window}")
+        if not isinstance(spec.latent_norm, RMSNormSpec) or spec.latent_norm.dim != spec.latent_dim:
+            raise ValueError("the latent vector's norm must be an RMS norm over latent_dim")
+        if not isinstance(spec.position, RopeSpec) or spec.position.rotary_dim != spec.rope_dim or spec.position.pairing != "half":
+            raise ValueError("latent attention rotates all rope_dim channels of the rotated parts, channel i with i + rope_dim / 2")
+        heads, dim, rope = spec.num_heads, spec.head_dim, spec.rope_dim
+        # One product for everything that reads the mixer's input: queries, the gate, the latent's down-projection.
+        rows = [tensors["q_proj"]] + ([tensors["gate_proj"]] if spec.gated else []) + [tensors["down_proj"]]
+        self.in_proj = runtime.matrix(torch.cat(rows, dim=0))
+        self.q_width = heads * (dim + rope)
+        self.gate_width = heads * spec.value_dim if spec.gated else 0
+        self.key_up = runtime.matrix(tensors["key_up_proj"].reshape(heads, dim, spec.latent_dim))        # [head][channel][latent]
+        self.value_up = runtime.matrix(tensors["value_up_proj"].reshape(heads, spec.value_dim, spec.latent_dim))
+        self.out_proj = runtime.matrix(tensors["out_proj"])
+        self.latent_norm = runtime.vector(tensors["latent_norm"])
+        self.position = build_part(spec.position, {}, runtime)
+        self.scale = spec.scale if spec.scale is not None else (dim + rope) ** -0.5
+
+    @classmethod
+    def tensor_decls(cls, spec: LatentAttentionSpec) -> dict[str, TensorDecl]:
+        heads = spec.num_heads
+        decls = {
+            "q_proj": TensorDecl((heads * (spec.head_dim + spec.rope_dim), spec.model_dim)),
+            "down_proj": TensorDecl((spec.latent_dim + spec.rope_dim, spec.model_dim)),
+            "latent_norm": TensorDecl((spec.latent_dim,), role="vector", init="ones"),
+            "key_up_proj": TensorDecl((heads * spec.head_dim, spec.latent_dim)),
+            "value_up_proj": TensorDecl((heads * spec.value_dim, spec.latent_dim)),
+            "out_proj": TensorDecl((spec.model_dim, heads * spec.value_dim)),
+        }
+        if spec.gated:
+            decls["gate_proj"] = TensorDecl((heads * spec.value_dim, spec.model_dim))
+        return decls
+
+    def cache_need(self) -> CacheNeed | None:
+        spec = self.spec
+        return PagedKVNeed(num_groups=1, head_dim=spec.latent_dim + spec.rope_dim, window=spec.window, value_dim=spec.latent_dim, values_in_keys=True)
+
+    can_accumulate = True
+
+    def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
+        spec, runtime = self.spec, self.runtime
+        heads, dim, rope, latent = spec.num_heads, spec.head_dim, spec.rope_dim, spec.latent_dim
+        tokens = step.tokens
+        projected = ops.linear(x, self.in_proj, status=runtime.status)
+        q = projected[:, : self.q_width]
+        gate = projected[:, self.q_width : self.q_width + self.gate_width] if spec.gated else None
+        down = projected[:, self.q_width + self.gate_width :]
+        # the heads' unrotated query parts into the latent's space: [head][token][latent]
+        q_plain = q.view(tokens, heads, dim + rope)[:, :, :dim].transpose(0, 1)
+        q_latent = ops.heads_linear(q_plain, self.key_up)
+        queries = runtime.empty(tokens, heads, latent + rope)
+        ops.latent_prepare(q, q_latent, down, queries, cache.k_pages, norm_weight=self.latent_norm, eps=spec.latent_norm.eps,
+                           scale_offset=spec.latent_norm.scale_offset, inv_freq=self.position.inv_freq, positions=step.positions,
+                           token_segment=step.token_segment, block_table=cache.block_table, num_heads=heads, head_dim=dim, latent=latent, rope=rope,
+                           write_kv=cache.owns, status=runtime.status)
+        summed = runtime.empty(tokens, heads, latent)
+        ops.latent_attention_plain(queries, cache.k_pages, summed, positions=step.positions, token_segment=step.token_segment,
+                                   block_table=cache.block_table, num_heads=heads, latent=latent, rope=rope, scale=self.scale, window=spec.window,
+                                   status=runtime.status)
+        values = ops.heads_linear(summed.transpose(0, 1), self.value_up, transpose_weight=True)   # [head][token][vdim]
+        mixed = runtime.empty(tokens, heads * spec.value_dim)
+        ops.gate_heads(values, gate, mixed)
+        if residual is not None:
+            return ops.linear_accumulate(mixed, self.out_proj, residual, status=runtime.status)
+        return ops.linear(mixed, self.out_proj, status=runtime.status)

@@ -107,6 +107,15 @@ class DecoderModel:
         residual = self.embedding.forward(step.token_ids, step.tokens)
         pending: torch.Tensor | None = None
         for position, entry in enumerate(self.plan.schedule):
+            if entry.add_embedding:
+                if pending is not None:
+                    ops.residual_add(residual, pending)
+                    pending = None
+                step.carry.clear()   # what a block left for its successor described the stream before this sum
+                self.embedding.add_to(residual, step.token_ids)
+            # the norm the next block begins with, for a block that can compute it on its way out
+            following = self.plan.schedule[position + 1] if position + 1 < len(self.plan.schedule) else None
+            step.carry["next_norm"] = None if following is None or following.add_embedding else getattr(self.blocks[following.layer], "first_norm", None)
             pending = self.blocks[entry.layer].forward(residual, pending, step, caches[position])
         if step.wanted == 0:
             return runtime.empty(0, self.plan.vocab_size, dtype=torch.float32)

@@ -22,7 +22,8 @@ class RMSNorm(Norm):
 
     @classmethod
     def tensor_decls(cls, spec: RMSNormSpec) -> dict[str, TensorDecl]:
-        return {"scale": TensorDecl((spec.dim,), role="vector", init="ones")}
+        # a weight that is used as ``w + offset`` is stored around zero
+        return {"scale": TensorDecl((spec.dim,), role="vector", init="ones" if spec.scale_offset == 0.0 else "normal")}
 
     def _out(self, x: torch.Tensor, rows: torch.Tensor | None, num_rows: int | None) -> torch.Tensor:
         count = x.shape[0] if rows is None else (rows.numel() if num_rows is None else num_rows)
@@ -30,7 +31,7 @@ class RMSNorm(Norm):
 
     def forward(self, x: torch.Tensor, rows: torch.Tensor | None = None, num_rows: int | None = None) -> torch.Tensor:
         out = self._out(x, rows, num_rows)
-        ops.rmsnorm(x, self.scale, out, self.spec.eps, rows=rows, scale_offset=self.spec.scale_offset)
+        ops.rmsnorm(x, self.scale, out, self.spec.eps, rows=rows, scale_offset=self.spec.scale_offset, exact=self.spec.exact)
         return out
 
     def residual_forward(
@@ -50,10 +51,18 @@ class RMSNorm(Norm):
             rows=rows,
             scale_offset=self.spec.scale_offset,
             write_back=delta is not None and rows is None,
+            exact=self.spec.exact,
         )
         return out
 
-    def accumulate(self, residual: torch.Tensor, delta: "torch.Tensor | ops.ScaledSum", rounded: torch.Tensor | None = None) -> None:
+    def accumulate(self, residual: torch.Tensor, delta: "torch.Tensor | ops.ScaledSum", rounded: torch.Tensor | None = None,
+                   then: "RMSNorm | None" = None) -> None:
         """``residual += norm(delta)`` on the 32-bit stream, the norm itself in 32-bit too (no rounding of the
-        normalised value); ``rounded`` receives the new stream in the activation type."""
-        ops.norm_accumulate(residual, delta, self.scale, self.spec.eps, scale_offset=self.spec.scale_offset, rounded=rounded)
+        normalised value); ``rounded`` receives the new stream in the activation type or, with ``then`` (an exact RMS
+        norm), that norm of the new stream: the same kernel computes both norms."""
+        next_norm = None
+        if then is not None:
+            if not then.spec.exact or then.spec.dim != self.spec.dim:
+                raise ValueError("only an exact RMS norm of the same width can follow in the same kernel")
+            next_norm = (then.scale, then.spec.eps, then.spec.scale_offset)
+        ops.norm_accumulate(residual, delta, self.scale, self.spec.eps, scale_offset=self.spec.scale_offset, rounded=rounded, next_norm=next_norm)
