@@ -1,7 +1,7 @@
 """Typed configuration of the Tudulix architecture (``"architecture": "Tudulix"`` in ``config.json``).
 
 A decoder whose layers have a norm before and after each sublayer, ``x <- x + norm1b(mixer(norm1(x)));
-x <- x + norm2b(ff(norm2(x)))``, the norms' weights stored around zero (``1 + w``).  A layer's mixer is
+x <- x + norm2b(ff(norm2(x)))``, the norms' weights kept as offsets from one (``1 + w``).  A layer's mixer is
 softmax attention with grouped key/value heads, pairwise ("interleaved") rotation of part of each head and
 a sliding window, or latent attention: keys and values made from one normed latent vector per token plus
 one rotated key part shared by all heads, under a sliding window, with a sigmoid gate on the heads'

@@ -22,7 +22,7 @@ class RMSNorm(Norm):
 
     @classmethod
     def tensor_decls(cls, spec: RMSNormSpec) -> dict[str, TensorDecl]:
-        # a weight that is used as ``w + offset`` is stored around zero
+        # a weight that is used as ``w + offset`` is made small
         return {"scale": TensorDecl((spec.dim,), role="vector", init="ones" if spec.scale_offset == 0.0 else "normal")}
 
     def _out(self, x: torch.Tensor, rows: torch.Tensor | None, num_rows: int | None) -> torch.Tensor:

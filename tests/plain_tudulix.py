@@ -28,7 +28,7 @@ def rms_norm(x, weight, eps):
 
 
 def offset_norm(x, weight, eps):
-    """The layers' norm: its weight is stored around zero and used as ``1 + weight``."""
+    """The layers' norm: its weight is an offset from one, ``1 + weight``."""
     return rms_norm(x, 1.0 + weight, eps)
 
 
