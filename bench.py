@@ -308,7 +308,7 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
     layer (of a routed feed-forward the router and the experts a token uses), attention (a multiply-add per query, visible
     key and channel, for scores and for values, under the window if there is one), the delta rule's three passes over a
     head's state per token, and the read-out of the wanted rows."""
-    from lalamo_b200.config import AttentionSpec, GatedDeltaSpec, GatedMLPSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
+    from lalamo_b200.config import AttentionSpec, GatedDeltaSpec, GatedMLPSpec, LatentAttentionSpec, ParallelMixerSpec, RoutedMLPSpec, ShortConvSpec
 
     def mixer_flops(spec) -> float:
         if isinstance(spec, ParallelMixerSpec):
@@ -319,6 +319,13 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
             window = spec.window or tokens
             pairs = sum(min(position + 1, window + spec.keep_first) for position in range(tokens))
             return 2.0 * rows * spec.model_dim * tokens + 2.0 * spec.num_heads * (spec.head_dim + value_dim) * pairs
+        if isinstance(spec, LatentAttentionSpec):
+            # projections, the queries taken into the latent's space and the sums taken out of it, scores and sums over latent + rope channels
+            heads, full = spec.num_heads, spec.latent_dim + spec.rope_dim
+            rows = heads * (spec.head_dim + spec.rope_dim) + full + (heads * spec.value_dim if spec.gated else 0) + heads * spec.value_dim
+            window = spec.window or tokens
+            pairs = sum(min(position + 1, window) for position in range(tokens))
+            return 2.0 * rows * spec.model_dim * tokens + 2.0 * heads * (spec.head_dim + spec.value_dim) * spec.latent_dim * tokens + 2.0 * heads * (full + spec.latent_dim) * pairs
         if isinstance(spec, GatedDeltaSpec):
             inner = spec.num_heads * (spec.key_dim + spec.value_dim)
             rows = 2 * spec.num_groups * spec.key_dim + 2 * spec.num_heads * spec.value_dim + spec.num_heads + spec.decay_rank + spec.gate_rank
@@ -334,7 +341,7 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
         if isinstance(spec, GatedMLPSpec):
             return 2.0 * 3 * spec.model_dim * spec.hidden_dim * tokens
         if isinstance(spec, RoutedMLPSpec):
-            return 2.0 * (3 * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens
+            return 2.0 * (3 * spec.top * spec.hidden_dim + spec.num_experts) * spec.model_dim * tokens + ffn_flops(spec.shared)
         raise TypeError(f"no operation count for {type(spec).__name__}")
 
     total = 2.0 * plan.model_dim * plan.vocab_size * wanted_rows
@@ -344,9 +351,10 @@ def plan_flops(plan, tokens: int, wanted_rows: int = 1) -> float:
     return total
 
 
-def run_compare(arguments, peaks: dict, peak_source: str) -> int:
+def run_compare(arguments, peaks: dict, peak_source: str, families: tuple[str, str] = ("vuvulorn", "lfm2")) -> int:
     """`--config vuvulorn-compare`: the Vuvulorn shapes beside the LFM2 shapes of the same width and depth (random weights):
-    a prompt of 2,048 tokens in one step, and decode steps at batch 8 and 64 with 4,096 tokens behind every request."""
+    a prompt of 2,048 tokens in one step, and decode steps at batch 8 and 64 with 4,096 tokens behind every request.
+    `--config tudulix-compare`: the same for the Tudulix shapes beside the Vuvulorn shapes."""
     import torch
 
     from lalamo_b200.config import config_from_dict
@@ -361,7 +369,7 @@ def run_compare(arguments, peaks: dict, peak_source: str) -> int:
     rows = []
     for size in arguments.compare_sizes.split(","):
         record = {"size": size}
-        for family in ("vuvulorn", "lfm2"):
+        for family in families:
             preset = f"{family}-{size}"
             config = config_from_dict(PRESETS[preset])
             engine = Engine.random(config, seed=7, std=0.02, engine_config=EngineConfig(
@@ -384,7 +392,7 @@ def run_compare(arguments, peaks: dict, peak_source: str) -> int:
             del engine
             torch.cuda.empty_cache()
         rows.append(record)
-    print(json.dumps({"config": "vuvulorn-compare", "prompt_tokens": prompt, "context": context, "dtype": "bf16",
+    print(json.dumps({"config": f"{families[0]}-compare", "prompt_tokens": prompt, "context": context, "dtype": "bf16",
                       "data": "synthetic: random bf16 weights N(0,0.02), random token ids, random cache contents", "peaks": peak_source,
                       "sizes": rows, "clocks": clocks.stop()}))
     return 0
@@ -527,8 +535,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=500)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare measures")
-    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare"],
+    parser.add_argument("--compare-sizes", default="350m,1.2b", help="the sizes --config vuvulorn-compare and tudulix-compare measure")
+    parser.add_argument("--config", default="lfm2-1.2b-decode", choices=["lfm2-1.2b-decode", "lfm2-350m-mixed", "lfm2-700m-long", "vuvulorn-compare", "tudulix-compare"],
                         help="lfm2-1.2b-decode (default): the decode step and its points; lfm2-350m-mixed: 64 requests with prompts of 128 to 2,048 "
                              "tokens and 256 new tokens through the scheduler; lfm2-700m-long: 16,384-token prompts at batch 1 and 8, then 512 decode steps")
     parser.add_argument("--batch", type=int, default=8)
@@ -567,6 +575,8 @@ def main() -> int:
         return run_long(arguments, peaks, peak_source)
     if arguments.config == "vuvulorn-compare":
         return run_compare(arguments, peaks, peak_source)
+    if arguments.config == "tudulix-compare":
+        return run_compare(arguments, peaks, peak_source, families=("tudulix", "vuvulorn"))
     if arguments.requests:
         requests, prompt_length, new_tokens = (int(part) for part in arguments.requests.split(","))
         engine, config = build_engine(max_tokens=requests * (prompt_length + new_tokens + 64), max_requests=max(requests, 2), max_batch_tokens=2048)

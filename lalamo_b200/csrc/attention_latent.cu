@@ -182,6 +182,276 @@ __global__ void gate_heads_kernel(const T* __restrict__ values, const T* __restr
     }
 }
 
+
+// ------------------------------------------------------------------------------- tensor cores
+// The same attention on mma.sync (bfloat16, 32-bit accumulation) for latent + rope and latent multiples of 16.
+//
+// A CTA of four warps takes one item: up to 64 query rows = consecutive tokens of one request x a block of heads,
+// 16 rows a warp.  All rows share the cached rows (there is one "key head"), which come through shared memory in blocks
+// of 64 rows (cp.async, two buffers) that start at multiples of 64 from the request's first token, so the order of a
+// query's sums does not depend on how the prompt was cut or on what shares its CTA.  A block serves both products: as
+// K for S = Q K^T over latent + rope channels (ldmatrix), and, its first `latent` channels, as V for O += P V
+// (ldmatrix.trans).  Rows that no query of the item sees are zero-filled, never read.  grid.z shares out the latent's
+// channels in chunks of 128 (every chunk computes the scores again); grid.y = head blocks x key splits: with splits > 1
+// every CTA takes a share of the item's blocks and leaves (maximum, sum, unnormalised O) for latent_merge_kernel.
+constexpr int kLatentMmaRows = 64, kLatentMmaKeys = 64, kLatentMmaChunk = 128, kLatentMmaThreads = 128;
+
+struct LatentMmaParams {
+    const __nv_bfloat16* q;       // [tokens][heads][latent + rope]
+    const __nv_bfloat16* pages;   // [page][row][latent + rope]
+    __nv_bfloat16* out;           // [tokens][heads][latent]
+    float* partial;               // splits > 1: [tokens][heads][split][latent + 2] (O unnormalised, maximum in base-2 units, sum)
+    const int* items;             // [num_items][2]: first token row, count
+    const int* positions;
+    const int* token_segment;
+    const int* block_table;
+    LatentLayout layout;
+    int num_heads, heads_per_cta, tokens_per_cta, head_blocks, splits, window;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ void latent_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* shared_address) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_address));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* shared_address) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_address));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+
+// 16 bytes from global to shared memory, or 16 zero bytes (nothing is read) if `valid` is false.
+__device__ __forceinline__ void latent_copy_16(void* shared_destination, const void* global_source, bool valid) {
+    const uint32_t destination = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(destination), "l"(global_source), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ float latent_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t latent_pack(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+__global__ void __launch_bounds__(kLatentMmaThreads)
+latent_attention_mma_kernel(LatentMmaParams p) {
+    extern __shared__ __align__(16) unsigned char latent_shared[];
+    const int latent = p.layout.latent, full = p.layout.latent + p.layout.rope;
+    const int pitch = full + 8;   // elements: rows 16 bytes apart modulo 128, so that ldmatrix meets no bank twice
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(latent_shared);          // [64][pitch]
+    __nv_bfloat16* k_s = q_s + kLatentMmaRows * pitch;                             // [2][64][pitch]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int item = blockIdx.x;
+    const int head_block = blockIdx.y / p.splits, split = blockIdx.y - head_block * p.splits;
+    const int chunk0 = blockIdx.z * kLatentMmaChunk;
+    const int chunk = min(kLatentMmaChunk, latent - chunk0);   // a multiple of 16
+    const int first_token = p.items[2 * item], count = p.items[2 * item + 1];
+    const int head0 = head_block * p.heads_per_cta;
+    const int heads_here = min(p.heads_per_cta, p.num_heads - head0);
+    const int rows_used = count * heads_here;
+    const int segment = p.token_segment[first_token];
+    const int position0 = p.positions[first_token];
+    const int last_position = position0 + count - 1;
+    const int lowest = p.window > 0 ? max(0, position0 - p.window + 1) : 0;   // the lowest row any query of the item sees
+    // this CTA's share of the item's blocks of 64 rows
+    const int block_lo = lowest / kLatentMmaKeys, block_hi = last_position / kLatentMmaKeys + 1;
+    const int per_split = (block_hi - block_lo + p.splits - 1) / p.splits;
+    const int block_begin = block_lo + split * per_split, block_end = min(block_hi, block_begin + per_split);
+
+    // queries: row r = (token r / heads_here, head head0 + r % heads_here); rows past rows_used are zero
+    const int chunks_per_row = full / 8;
+    for (int c = tid; c < kLatentMmaRows * chunks_per_row; c += kLatentMmaThreads) {
+        const int r = c / chunks_per_row, piece = c - r * chunks_per_row;
+        const bool valid = r < rows_used;
+        const int token = first_token + (valid ? r / heads_here : 0), head = head0 + (valid ? r % heads_here : 0);
+        latent_copy_16(q_s + r * pitch + piece * 8, p.q + (static_cast<size_t>(token) * p.num_heads + head) * full + piece * 8, valid);
+    }
+    auto load_block = [&](int block, int stage) {
+        __nv_bfloat16* dst = k_s + stage * kLatentMmaKeys * pitch;
+        const int key0 = block * kLatentMmaKeys;
+        for (int c = tid; c < kLatentMmaKeys * chunks_per_row; c += kLatentMmaThreads) {
+            const int r = c / chunks_per_row, piece = c - r * chunks_per_row;
+            const int key = key0 + r;
+            bool valid = key >= lowest && key <= last_position;
+            const __nv_bfloat16* src = p.pages;
+            if (valid) {
+                const int table_column = key / p.layout.page_size;
+                const int page = table_column < p.layout.max_blocks ? p.block_table[static_cast<size_t>(segment) * p.layout.max_blocks + table_column] : -1;
+                if (page < 0 || page >= p.layout.num_pages) {
+                    if (piece == 0) report_error(p.status, kBadPage);
+                    valid = false;
+                } else {
+                    src = p.pages + (static_cast<size_t>(page) * p.layout.page_size + (key - table_column * p.layout.page_size)) * full + piece * 8;
+                }
+            }
+            latent_copy_16(dst + r * pitch + piece * 8, src, valid);
+        }
+    };
+    if (block_begin < block_end) load_block(block_begin, 0);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+
+    const int g = lane >> 2, t = lane & 3;
+    const int row_a = warp * 16 + g, row_b = row_a + 8;   // this thread's two rows of the CTA's 64
+    const bool warp_active = warp * 16 < rows_used;
+    const int position_a = position0 + (row_a < rows_used ? row_a / heads_here : 0);
+    const int position_b = position0 + (row_b < rows_used ? row_b / heads_here : 0);
+    const int first_a = p.window > 0 ? max(0, position_a - p.window + 1) : 0;
+    const int first_b = p.window > 0 ? max(0, position_b - p.window + 1) : 0;
+    float o[kLatentMmaChunk / 8][4];
+#pragma unroll
+    for (int j = 0; j < kLatentMmaChunk / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float max_a = -INFINITY, max_b = -INFINITY, sum_a = 0.0f, sum_b = 0.0f;   // maxima of the raw scores
+
+    for (int block = block_begin; block < block_end; ++block) {
+        const int stage = (block - block_begin) & 1;
+        if (block + 1 < block_end) load_block(block + 1, stage ^ 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        __syncthreads();
+        if (warp_active) {
+            const __nv_bfloat16* k_block = k_s + stage * kLatentMmaKeys * pitch;
+            float s[kLatentMmaKeys / 8][4];
+#pragma unroll
+            for (int j = 0; j < kLatentMmaKeys / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+            for (int k0 = 0; k0 < full; k0 += 16) {
+                uint32_t a[4];
+                ldmatrix_x4(a, q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + k0 + (lane >> 4) * 8);
+#pragma unroll
+                for (int j = 0; j < kLatentMmaKeys / 16; ++j) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, k_block + (j * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + k0 + ((lane >> 3) & 1) * 8);
+                    latent_mma(s[2 * j], a, b[0], b[1]);
+                    latent_mma(s[2 * j + 1], a, b[2], b[3]);
+                }
+            }
+            // masks, and the block's maxima per row
+            const int key0 = block * kLatentMmaKeys;
+            float block_max_a = -INFINITY, block_max_b = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kLatentMmaKeys / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key0 + 8 * j + 2 * t + e;
+                    if (key < first_a || key > position_a) s[j][e] = -INFINITY;
+                    if (key < first_b || key > position_b) s[j][2 + e] = -INFINITY;
+                    block_max_a = fmaxf(block_max_a, s[j][e]);
+                    block_max_b = fmaxf(block_max_b, s[j][2 + e]);
+                }
+            }
+            block_max_a = fmaxf(block_max_a, __shfl_xor_sync(0xffffffffu, block_max_a, 1));
+            block_max_a = fmaxf(block_max_a, __shfl_xor_sync(0xffffffffu, block_max_a, 2));
+            block_max_b = fmaxf(block_max_b, __shfl_xor_sync(0xffffffffu, block_max_b, 1));
+            block_max_b = fmaxf(block_max_b, __shfl_xor_sync(0xffffffffu, block_max_b, 2));
+            const float new_a = fmaxf(max_a, block_max_a), new_b = fmaxf(max_b, block_max_b);
+            const float shift_a = new_a == -INFINITY ? 0.0f : new_a * p.scale_log2, shift_b = new_b == -INFINITY ? 0.0f : new_b * p.scale_log2;
+            const float keep_a = max_a == -INFINITY ? 0.0f : latent_exp2(max_a * p.scale_log2 - shift_a);
+            const float keep_b = max_b == -INFINITY ? 0.0f : latent_exp2(max_b * p.scale_log2 - shift_b);
+            max_a = new_a;
+            max_b = new_b;
+            float add_a = 0.0f, add_b = 0.0f;
+            uint32_t prob[kLatentMmaKeys / 16][4];   // P as the second product's first operand
+#pragma unroll
+            for (int j = 0; j < kLatentMmaKeys / 8; ++j) {
+                const float p0 = latent_exp2(s[j][0] * p.scale_log2 - shift_a), p1 = latent_exp2(s[j][1] * p.scale_log2 - shift_a);
+                const float p2 = latent_exp2(s[j][2] * p.scale_log2 - shift_b), p3 = latent_exp2(s[j][3] * p.scale_log2 - shift_b);
+                // the sums add what the product uses: the rounded probabilities
+                const __nv_bfloat162 low = __floats2bfloat162_rn(p0, p1), high = __floats2bfloat162_rn(p2, p3);
+                add_a += __low2float(low) + __high2float(low);
+                add_b += __low2float(high) + __high2float(high);
+                prob[j >> 1][(j & 1) * 2] = *reinterpret_cast<const uint32_t*>(&low);
+                prob[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&high);
+            }
+            sum_a = sum_a * keep_a + add_a;
+            sum_b = sum_b * keep_b + add_b;
+#pragma unroll
+            for (int j = 0; j < kLatentMmaChunk / 8; ++j) {
+                o[j][0] *= keep_a;
+                o[j][1] *= keep_a;
+                o[j][2] *= keep_b;
+                o[j][3] *= keep_b;
+            }
+#pragma unroll
+            for (int kk = 0; kk < kLatentMmaKeys / 16; ++kk) {
+#pragma unroll
+                for (int j = 0; j < kLatentMmaChunk / 16; ++j) {
+                    if (16 * j < chunk) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, k_block + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + chunk0 + j * 16 + (lane >> 4) * 8);
+                        latent_mma(o[2 * j], prob[kk], b[0], b[1]);
+                        latent_mma(o[2 * j + 1], prob[kk], b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();   // the buffer is reloaded by the next round's copies
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    if (!warp_active) return;
+    // a row's sum lies in the four lanes of its quad
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = half == 0 ? row_a : row_b;
+        if (row >= rows_used) continue;
+        const int token = first_token + row / heads_here, head = head0 + row % heads_here;
+        const float sum = half == 0 ? sum_a : sum_b, top = half == 0 ? max_a : max_b;
+        if (p.splits == 1) {
+            const float norm = sum > 0.0f ? 1.0f / sum : 0.0f;
+            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.num_heads + head) * latent + chunk0;
+#pragma unroll
+            for (int j = 0; j < kLatentMmaChunk / 8; ++j)
+                if (8 * j < chunk) *reinterpret_cast<uint32_t*>(dst + 8 * j + 2 * t) = latent_pack(o[j][2 * half] * norm, o[j][2 * half + 1] * norm);
+        } else {
+            float* dst = p.partial + ((static_cast<size_t>(token) * p.num_heads + head) * p.splits + split) * (latent + 2);
+#pragma unroll
+            for (int j = 0; j < kLatentMmaChunk / 8; ++j)
+                if (8 * j < chunk) *reinterpret_cast<float2*>(dst + chunk0 + 8 * j + 2 * t) = make_float2(o[j][2 * half], o[j][2 * half + 1]);
+            if (t == 0 && blockIdx.z == 0) {
+                dst[latent] = top == -INFINITY ? -INFINITY : top * p.scale_log2;
+                dst[latent + 1] = sum;
+            }
+        }
+    }
+}
+
+// out[token][head] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits, in split order.  One block per (token, head).
+__global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int latent) {
+    const size_t row = blockIdx.x;
+    const float* mine = partial + row * splits * (latent + 2);
+    float top = -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, mine[s * (latent + 2) + latent]);
+    float total = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = mine[s * (latent + 2) + latent];
+        if (m != -INFINITY) total += exp2f(m - top) * mine[s * (latent + 2) + latent + 1];
+    }
+    const float norm = total > 0.0f ? 1.0f / total : 0.0f;
+    for (int d = threadIdx.x; d < latent; d += blockDim.x) {
+        float sum = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = mine[s * (latent + 2) + latent];
+            if (m != -INFINITY) sum += exp2f(m - top) * mine[s * (latent + 2) + d];
+        }
+        out[row * latent + d] = __float2bfloat16_rn(sum * norm);
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -218,6 +488,47 @@ int lb_latent_attention_plain(const void* q, const void* pages, void* out, const
             static_cast<const T*>(q), static_cast<const T*>(pages), static_cast<T*>(out), positions, token_segment, block_table, layout, num_heads, scale,
             window, status);
     })
+    return LB_LAUNCH_RESULT();
+}
+
+// bfloat16; latent and rope multiples of 16, page sizes that are multiples of 16.  items: [num_items][2] (first token row, count),
+// each at most tokens_per_cta consecutive tokens of one request; heads_per_cta * tokens_per_cta <= 64.  partial: splits > 1 only,
+// [tokens][heads][splits][latent + 2] floats.  Returns -2 for sizes it does not take.
+int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* partial, const int* items, int num_items, const int* positions,
+                            const int* token_segment, const int* block_table, int tokens, int num_heads, int latent, int rope, int page_size,
+                            int num_pages, int max_blocks, float scale, int window, int heads_per_cta, int tokens_per_cta, int splits, int* status,
+                            cudaStream_t stream) {
+    if (num_items == 0 || tokens == 0) return 0;
+    if (latent < 16 || latent % 16 != 0 || rope % 16 != 0 || page_size % 16 != 0 || heads_per_cta < 1 || tokens_per_cta < 1 ||
+        heads_per_cta * tokens_per_cta > lb::kLatentMmaRows || splits < 1 || (splits > 1 && partial == nullptr))
+        return -2;
+    const int full = latent + rope;
+    const size_t shared = static_cast<size_t>(3) * lb::kLatentMmaRows * (full + 8) * sizeof(__nv_bfloat16);
+    if (shared > 227 * 1024) return -2;
+    static lb::OncePerDevice once;
+    const cudaError_t allowed = lb::allow_shared_memory(once, lb::latent_attention_mma_kernel, 227 * 1024);
+    if (allowed != cudaSuccess) return static_cast<int>(allowed);
+    lb::LatentMmaParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.pages = static_cast<const __nv_bfloat16*>(pages);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.partial = partial;
+    p.items = items;
+    p.positions = positions;
+    p.token_segment = token_segment;
+    p.block_table = block_table;
+    p.layout = lb::LatentLayout{page_size, num_pages, max_blocks, latent, rope};
+    p.num_heads = num_heads;
+    p.heads_per_cta = heads_per_cta;
+    p.tokens_per_cta = tokens_per_cta;
+    p.head_blocks = (num_heads + heads_per_cta - 1) / heads_per_cta;
+    p.splits = splits;
+    p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = status;
+    const dim3 grid(num_items, p.head_blocks * splits, (latent + lb::kLatentMmaChunk - 1) / lb::kLatentMmaChunk);
+    lb::latent_attention_mma_kernel<<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
+    if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, 0, stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
     return LB_LAUNCH_RESULT();
 }
 

@@ -127,6 +127,25 @@ def _vuvulorn_shape(width: int, layers: int, left_heads: int, left_kv_heads: int
     }
 
 
+def _tudulix_shape(width: int, layers: int, heads: int, kv_heads: int, ff: int, experts: int, top: int, rank: int) -> dict[str, Any]:
+    """A Tudulix shape for the random-weights mode: grouped attention with heads of 64 under a window of 1,024 tokens in turn
+    with latent attention (heads of 64 + 32 rotated channels over a latent of ``rank``) under a window of 2,048, every layer
+    with ``top`` routed experts of ``ff`` columns and a shared one of as many; the third and fourth layer run twice."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": {"dims": 64, "base": 1000000.0}}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": rank, "scale": 96 ** -0.5, "mask": {"size": 2048}, "rot": {"dims": 32, "base": 10000.0}}
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff, "limit": 7.0}}
+    return {
+        "architecture": "Tudulix",
+        "vocab": 65536,
+        "width": width,
+        "norm": {"eps": 1e-6},
+        "embedding": {"scale": float(width) ** 0.5},
+        "logit_scale": 1.0,
+        "loop": {"start": 2, "stop": 4, "times": 2},
+        "layers": [{"type": "latent_attention" if index % 2 else "attention", "mixer": latent if index % 2 else attention, "mlp": mlp} for index in range(layers)],
+    }
+
+
 # Shapes of the published checkpoints, and Vuvulorn shapes of the same widths and depths, for the random-weights mode
 # (no weights are downloaded).
 PRESETS: dict[str, dict[str, Any]] = {
@@ -135,4 +154,7 @@ PRESETS: dict[str, dict[str, Any]] = {
     "lfm2-1.2b": _lfm2_shape(2048, 32, 12288),
     "vuvulorn-350m": _vuvulorn_shape(1024, 16, 16, 4, 8, 64, 128, 4608, 16, 4, 64),
     "vuvulorn-1.2b": _vuvulorn_shape(2048, 16, 16, 4, 8, 128, 128, 8192, 16, 4, 64),
+    # 14 layers of which two run twice: 16 layer runs, and per token as many feed-forward columns (3 routed experts + the shared one) as the shapes above
+    "tudulix-350m": _tudulix_shape(1024, 14, 16, 4, 1152, 16, 3, 256),
+    "tudulix-1.2b": _tudulix_shape(2048, 14, 16, 4, 2048, 16, 3, 256),
 }

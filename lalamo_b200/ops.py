@@ -932,6 +932,56 @@ def latent_attention_plain(q: torch.Tensor, pages: torch.Tensor, out: torch.Tens
     _done(code, "latent_attention_plain")
 
 
+LATENT_MMA_ROWS = 64  # query rows (tokens x heads) of one CTA of the tensor-core latent attention
+
+
+def latent_attention_supported(dtype: torch.dtype, latent: int, rope: int, page_size: int) -> bool:
+    """Whether :func:`latent_attention` (tensor cores) takes these sizes; :func:`latent_attention_plain` takes the rest."""
+    return dtype == torch.bfloat16 and latent >= 16 and latent % 16 == 0 and rope % 16 == 0 and page_size % 16 == 0 and 3 * 64 * (latent + rope + 8) * 2 <= 227 * 1024
+
+
+def latent_attention_tiling(num_heads: int) -> tuple[int, int]:
+    """``(heads, tokens)`` of one CTA's query rows: all heads of as many consecutive tokens as fit (blocks of 64 heads beyond that)."""
+    heads = min(num_heads, LATENT_MMA_ROWS)
+    return heads, max(1, LATENT_MMA_ROWS // heads)
+
+
+def latent_attention_splits(num_items: int, num_heads: int, latent: int, window: int | None, max_context: int, sms: int | None = None) -> int:
+    """Over how many CTAs an item's cached rows are shared out: 1 where the items fill the GPU by themselves."""
+    heads, tokens = latent_attention_tiling(num_heads)
+    ctas = num_items * -(-num_heads // heads) * -(-latent // 128)
+    sms = sms or sm_count()
+    rows = min(window, max_context) if window else max_context
+    blocks = -(-(rows + tokens) // 64) + 1
+    if ctas >= 2 * sms or blocks <= 2:
+        return 1
+    return max(1, min(blocks // 2, -(-2 * sms // ctas), 32))
+
+
+def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *, items: torch.Tensor, num_items: int, positions: torch.Tensor,
+                     token_segment: torch.Tensor, block_table: torch.Tensor, num_heads: int, latent: int, rope: int, scale: float, window: int | None,
+                     status: torch.Tensor, splits: int = 1) -> None:
+    """:func:`latent_attention_plain` on the tensor cores (bfloat16).  ``items``: int32 ``[num_items, 2]`` (first token row,
+    count), each at most ``latent_attention_tiling(num_heads)[1]`` consecutive tokens of one request, together all tokens.
+    ``splits`` > 1 shares an item's cached rows out over that many CTAs, merged in split order."""
+    _check(q, "q", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    _check(items, "items", torch.int32)
+    tokens = q.shape[0]
+    if q.shape != (tokens, num_heads, latent + rope) or out.shape != (tokens, num_heads, latent) or items.numel() < 2 * num_items:
+        raise KernelError("latent_attention: q must be [tokens, heads, latent + rope], out [tokens, heads, latent], items [num_items, 2]")
+    page_size, num_pages, max_blocks = _check_latent_pages(pages, block_table, latent, rope)
+    if pages.dtype != q.dtype or not latent_attention_supported(q.dtype, latent, rope, page_size):
+        raise KernelError(f"latent_attention: latent {latent}, rope {rope}, pages of {page_size} are not sizes the tensor-core kernel takes")
+    heads_per_cta, tokens_per_cta = latent_attention_tiling(num_heads)
+    partial = torch.empty(tokens, num_heads, splits, latent + 2, dtype=torch.float32, device=q.device) if splits > 1 else None
+    code = _lib().lb_latent_attention_mma(_ptr(q), _ptr(pages), _ptr(out), _ptr(partial), _ptr(items), c_int(num_items), _ptr(positions), _ptr(token_segment),
+                                          _ptr(block_table), c_int(tokens), c_int(num_heads), c_int(latent), c_int(rope), c_int(page_size), c_int(num_pages),
+                                          c_int(max_blocks), c_float(scale), c_int(window if window else 0), c_int(heads_per_cta), c_int(tokens_per_cta),
+                                          c_int(splits), _ptr(status), _stream())
+    _done(code, "latent_attention_mma", 2 if splits > 1 else 1)
+
+
 def gate_heads(values: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) -> None:
     """``out[t, h * vdim + j] = values[h, t, j] * sigmoid(gate[t, h * vdim + j])`` (``gate=None``: no gate); ``gate`` may
     be a column slice of a wider product."""

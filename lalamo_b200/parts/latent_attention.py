@@ -10,11 +10,12 @@ from __future__ import annotations
 
 from typing import Mapping
 
+import numpy as np
 import torch
 
 from .. import ops
 from ..config.plan import LatentAttentionSpec, RMSNormSpec, RopeSpec
-from .base import CacheNeed, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
+from .base import CacheNeed, HostSegments, Mixer, PagedKVNeed, PagedKVView, Runtime, StepInputs, TensorDecl, build_part, register_part
 
 __all__ = ["LatentAttention"]
 
@@ -63,6 +64,19 @@ class LatentAttention(Mixer):
         spec = self.spec
         return PagedKVNeed(num_groups=1, head_dim=spec.latent_dim + spec.rope_dim, window=spec.window, value_dim=spec.latent_dim, values_in_keys=True)
 
+    # The tensor-core kernel's items depend on where the portions start and how long they are, not on what the cache
+    # holds, and they are the same for every latent layer with as many heads.
+    step_plan_uses_context = False
+
+    def step_plan_key(self) -> object:
+        return ("latent_attention", ops.latent_attention_tiling(self.spec.num_heads))
+
+    def plan_step(self, segments: HostSegments) -> dict[str, np.ndarray]:
+        """``items``: ``(first row, count)`` of every run of consecutive tokens that one CTA takes."""
+        _, run = ops.latent_attention_tiling(self.spec.num_heads)
+        items = [(first, min(run, start + length - first)) for start, length in zip(segments.start, segments.length) for first in range(start, start + length, run)]
+        return {"items": np.asarray(items, dtype=np.int32).reshape(-1)}
+
     can_accumulate = True
 
     def forward(self, x: torch.Tensor, step: StepInputs, cache: PagedKVView, residual: torch.Tensor | None = None) -> torch.Tensor | None:  # type: ignore[override]
@@ -82,9 +96,15 @@ class LatentAttention(Mixer):
                            token_segment=step.token_segment, block_table=cache.block_table, num_heads=heads, head_dim=dim, latent=latent, rope=rope,
                            write_kv=cache.owns, status=runtime.status)
         summed = runtime.empty(tokens, heads, latent)
-        ops.latent_attention_plain(queries, cache.k_pages, summed, positions=step.positions, token_segment=step.token_segment,
-                                   block_table=cache.block_table, num_heads=heads, latent=latent, rope=rope, scale=self.scale, window=spec.window,
-                                   status=runtime.status)
+        common = dict(positions=step.positions, token_segment=step.token_segment, block_table=cache.block_table, num_heads=heads, latent=latent, rope=rope,
+                      scale=self.scale, window=spec.window, status=runtime.status)
+        if ops.latent_attention_supported(runtime.dtype, latent, rope, cache.k_pages.shape[1]):
+            lists, host_lists = step.plan_of(self)
+            num_items = host_lists["items"].size // 2
+            splits = ops.latent_attention_splits(num_items, heads, latent, spec.window, step.max_context)
+            ops.latent_attention(queries, cache.k_pages, summed, items=lists["items"], num_items=num_items, splits=splits, **common)
+        else:
+            ops.latent_attention_plain(queries, cache.k_pages, summed, **common)
         values = ops.heads_linear(summed.transpose(0, 1), self.value_up, transpose_weight=True)   # [head][token][vdim]
         mixed = runtime.empty(tokens, heads * spec.value_dim)
         ops.gate_heads(values, gate, mixed)

@@ -445,6 +445,45 @@ def test_latent_attention_edges_with_one_row_that_stands_out(latent, rope, heads
             assert want[inside, :, 0].min() > 25 and np.abs(want[positions.index(special + window)]).max() < 5
 
 
+@pytest.mark.parametrize("splits", [1, 3, 32])
+@pytest.mark.parametrize("latent,rope,heads,window,special", [(64, 32, 4, 37, 100), (128, 64, 8, 150, 249), (256, 32, 16, 64, 0), (32, 16, 3, 1, 7), (144, 48, 5, 300, 63),
+                                                             (64, 0, 70, 129, 130)])
+def test_tensor_core_latent_attention_at_every_position(latent, rope, heads, window, special, splits):
+    """Every position of a 400-token request as a query on the tensor-core kernel, in one portion and cut into portions that
+    start anywhere (runs of tokens shorter than a CTA takes, single tokens), with the cached rows shared out over CTAs or not;
+    one row stands out wherever it is seen."""
+    from lalamo_b200 import ops
+
+    generator = np.random.default_rng(latent + window)
+    n, page_size, full, dtype = 400, 16, latent + rope, torch.bfloat16
+    rows = 0.3 * generator.standard_normal((n, full))
+    direction = generator.standard_normal(full)
+    direction[0] = 0.0
+    direction /= np.linalg.norm(direction)
+    rows[special] = 6.0 * direction
+    rows[special, 0] = 30.0
+    q = 0.3 * generator.standard_normal((n, heads, full)) + 4.0 * direction
+    q[..., 0] = 0.0
+    rows, q = (torch.from_numpy(a).to(dtype).double().numpy() for a in (rows, q))
+    want = plain_latent_sums(q, rows, list(range(n)), latent, 0.5, window)
+    pages, table = latent_rows_in_pages(rows, page_size, dtype, special)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    run = ops.latent_attention_tiling(heads)[1]
+    for portions in ([n], [1, 2, 3, 64, 1, 1, 100, 29, 199]):
+        out = torch.zeros(n, heads, latent, dtype=dtype, device="cuda")
+        starts = np.concatenate([[0], np.cumsum(portions)[:-1]])
+        items = [(first, min(run, start + length - first)) for start, length in zip(starts, portions) for first in range(start, start + length, run)]
+        ops.latent_attention(torch.from_numpy(q).to(dtype).cuda().contiguous(), pages, out, items=as_int(np.asarray(items).reshape(-1)), num_items=len(items),
+                             positions=torch.arange(n, dtype=torch.int32, device="cuda"), token_segment=torch.zeros(n, dtype=torch.int32, device="cuda"),
+                             block_table=table, num_heads=heads, latent=latent, rope=rope, scale=0.5, window=window, status=status, splits=splits)
+        got = out.float().cpu().numpy()
+        assert int(status.item()) == 0
+        worst = np.abs(got - want).max(axis=(1, 2))
+        assert worst.max() < 0.3, (portions, int(worst.argmax()), float(worst.max()))
+    if special + window < n:
+        assert want[special + window - 1, :, 0].min() > 25 and np.abs(want[special + window]).max() < 5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_latent_rows_and_queries_are_prepared_as_the_plain_implementation_does(dtype):
     """Norm of the latent, rotation of the shared key part and of the queries' rotated parts, written through a block table;
