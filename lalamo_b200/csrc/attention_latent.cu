@@ -192,9 +192,9 @@ __global__ void gate_heads_kernel(const T* __restrict__ values, const T* __restr
 // query's sums does not depend on how the prompt was cut or on what shares its CTA.  A block serves both products: as
 // K for S = Q K^T over latent + rope channels (ldmatrix), and, its first `latent` channels, as V for O += P V
 // (ldmatrix.trans).  Rows that no query of the item sees are zero-filled, never read.  grid.z shares out the latent's
-// channels in chunks of 128 (every chunk computes the scores again); grid.y = head blocks x key splits: with splits > 1
+// channels in chunks of CHUNK (128, or 256 for latents wider than 128; every chunk computes the scores again); grid.y = head blocks x key splits: with splits > 1
 // every CTA takes a share of the item's blocks and leaves (maximum, sum, unnormalised O) for latent_merge_kernel.
-constexpr int kLatentMmaRows = 64, kLatentMmaKeys = 64, kLatentMmaChunk = 128, kLatentMmaThreads = 128;
+constexpr int kLatentMmaRows = 64, kLatentMmaKeys = 64, kLatentMmaThreads = 128;
 
 struct LatentMmaParams {
     const __nv_bfloat16* q;       // [tokens][heads][latent + rope]
@@ -246,8 +246,10 @@ __device__ __forceinline__ uint32_t latent_pack(float low, float high) {
     return *reinterpret_cast<const uint32_t*>(&pair);
 }
 
+template <int CHUNK>
 __global__ void __launch_bounds__(kLatentMmaThreads)
 latent_attention_mma_kernel(LatentMmaParams p) {
+    constexpr int kLatentMmaChunk = CHUNK;
     extern __shared__ __align__(16) unsigned char latent_shared[];
     const int latent = p.layout.latent, full = p.layout.latent + p.layout.rope;
     const int pitch = full + 8;   // elements: rows 16 bytes apart modulo 128, so that ldmatrix meets no bank twice
@@ -273,17 +275,24 @@ latent_attention_mma_kernel(LatentMmaParams p) {
 
     // queries: row r = (token r / heads_here, head head0 + r % heads_here); rows past rows_used are zero
     const int chunks_per_row = full / 8;
-    for (int c = tid; c < kLatentMmaRows * chunks_per_row; c += kLatentMmaThreads) {
-        const int r = c / chunks_per_row, piece = c - r * chunks_per_row;
+    // a thread's pieces are 128 apart: (row, piece within the row) advance by these steps
+    const int row_step = kLatentMmaThreads / chunks_per_row, piece_step = kLatentMmaThreads - row_step * chunks_per_row;
+    const int first_r = tid / chunks_per_row, first_piece = tid - first_r * chunks_per_row;
+    for (int r = first_r, piece = first_piece; r < kLatentMmaRows;) {
         const bool valid = r < rows_used;
         const int token = first_token + (valid ? r / heads_here : 0), head = head0 + (valid ? r % heads_here : 0);
         latent_copy_16(q_s + r * pitch + piece * 8, p.q + (static_cast<size_t>(token) * p.num_heads + head) * full + piece * 8, valid);
+        r += row_step;
+        piece += piece_step;
+        if (piece >= chunks_per_row) {
+            piece -= chunks_per_row;
+            ++r;
+        }
     }
     auto load_block = [&](int block, int stage) {
         __nv_bfloat16* dst = k_s + stage * kLatentMmaKeys * pitch;
         const int key0 = block * kLatentMmaKeys;
-        for (int c = tid; c < kLatentMmaKeys * chunks_per_row; c += kLatentMmaThreads) {
-            const int r = c / chunks_per_row, piece = c - r * chunks_per_row;
+        for (int r = first_r, piece = first_piece; r < kLatentMmaKeys;) {
             const int key = key0 + r;
             bool valid = key >= lowest && key <= last_position;
             const __nv_bfloat16* src = p.pages;
@@ -298,6 +307,12 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 }
             }
             latent_copy_16(dst + r * pitch + piece * 8, src, valid);
+            r += row_step;
+            piece += piece_step;
+            if (piece >= chunks_per_row) {
+                piece -= chunks_per_row;
+                ++r;
+            }
         }
     };
     if (block_begin < block_end) load_block(block_begin, 0);
@@ -326,15 +341,35 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             float s[kLatentMmaKeys / 8][4];
 #pragma unroll
             for (int j = 0; j < kLatentMmaKeys / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-            for (int k0 = 0; k0 < full; k0 += 16) {
-                uint32_t a[4];
-                ldmatrix_x4(a, q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + k0 + (lane >> 4) * 8);
+            // a step's fragments are asked for before the step before's products are issued
+            const __nv_bfloat16* a_address = q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 8;
+            const __nv_bfloat16* b_address = k_block + ((lane & 7) + (lane >> 4) * 8) * pitch + ((lane >> 3) & 1) * 8;
+            uint32_t a[2][4], b[2][kLatentMmaKeys / 16][4];
+            ldmatrix_x4(a[0], a_address);
+#pragma unroll
+            for (int j = 0; j < kLatentMmaKeys / 16; ++j) ldmatrix_x4(b[0][j], b_address + j * 16 * pitch);
+            for (int k0 = 0; k0 < full; k0 += 32) {
+                if (k0 + 16 < full) {
+                    ldmatrix_x4(a[1], a_address + k0 + 16);
+#pragma unroll
+                    for (int j = 0; j < kLatentMmaKeys / 16; ++j) ldmatrix_x4(b[1][j], b_address + j * 16 * pitch + k0 + 16);
+                }
 #pragma unroll
                 for (int j = 0; j < kLatentMmaKeys / 16; ++j) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, k_block + (j * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + k0 + ((lane >> 3) & 1) * 8);
-                    latent_mma(s[2 * j], a, b[0], b[1]);
-                    latent_mma(s[2 * j + 1], a, b[2], b[3]);
+                    latent_mma(s[2 * j], a[0], b[0][j][0], b[0][j][1]);
+                    latent_mma(s[2 * j + 1], a[0], b[0][j][2], b[0][j][3]);
+                }
+                if (k0 + 16 < full) {
+                    if (k0 + 32 < full) {
+                        ldmatrix_x4(a[0], a_address + k0 + 32);
+#pragma unroll
+                        for (int j = 0; j < kLatentMmaKeys / 16; ++j) ldmatrix_x4(b[0][j], b_address + j * 16 * pitch + k0 + 32);
+                    }
+#pragma unroll
+                    for (int j = 0; j < kLatentMmaKeys / 16; ++j) {
+                        latent_mma(s[2 * j], a[1], b[1][j][0], b[1][j][1]);
+                        latent_mma(s[2 * j + 1], a[1], b[1][j][2], b[1][j][3]);
+                    }
                 }
             }
             // masks, and the block's maxima per row
@@ -383,15 +418,21 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                 o[j][2] *= keep_b;
                 o[j][3] *= keep_b;
             }
+            const __nv_bfloat16* v_address = k_block + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + chunk0 + (lane >> 4) * 8;
 #pragma unroll
             for (int kk = 0; kk < kLatentMmaKeys / 16; ++kk) {
 #pragma unroll
-                for (int j = 0; j < kLatentMmaChunk / 16; ++j) {
-                    if (16 * j < chunk) {
-                        uint32_t b[4];
-                        ldmatrix_x4_trans(b, k_block + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + chunk0 + j * 16 + (lane >> 4) * 8);
-                        latent_mma(o[2 * j], prob[kk], b[0], b[1]);
-                        latent_mma(o[2 * j + 1], prob[kk], b[2], b[3]);
+                for (int j = 0; j < kLatentMmaChunk / 16; j += 4) {   // four loads on their way before their products
+                    uint32_t v[4][4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (16 * (j + u) < chunk) ldmatrix_x4_trans(v[u], v_address + kk * 16 * pitch + (j + u) * 16);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (16 * (j + u) < chunk) {
+                            latent_mma(o[2 * (j + u)], prob[kk], v[u][0], v[u][1]);
+                            latent_mma(o[2 * (j + u) + 1], prob[kk], v[u][2], v[u][3]);
+                        }
                     }
                 }
             }
@@ -505,8 +546,10 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
     const int full = latent + rope;
     const size_t shared = static_cast<size_t>(3) * lb::kLatentMmaRows * (full + 8) * sizeof(__nv_bfloat16);
     if (shared > 227 * 1024) return -2;
-    static lb::OncePerDevice once;
-    const cudaError_t allowed = lb::allow_shared_memory(once, lb::latent_attention_mma_kernel, 227 * 1024);
+    static lb::OncePerDevice once_narrow, once_wide;
+    const bool wide = latent > 128;   // 256 channels of the sums per CTA: twice the accumulators, the scores computed half as often
+    const cudaError_t allowed = wide ? lb::allow_shared_memory(once_wide, lb::latent_attention_mma_kernel<256>, 227 * 1024)
+                                     : lb::allow_shared_memory(once_narrow, lb::latent_attention_mma_kernel<128>, 227 * 1024);
     if (allowed != cudaSuccess) return static_cast<int>(allowed);
     lb::LatentMmaParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -526,8 +569,13 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = status;
-    const dim3 grid(num_items, p.head_blocks * splits, (latent + lb::kLatentMmaChunk - 1) / lb::kLatentMmaChunk);
-    lb::latent_attention_mma_kernel<<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
+    const int chunk = wide ? 256 : 128;
+    const dim3 grid(num_items, p.head_blocks * splits, (latent + chunk - 1) / chunk);
+    if (wide) {
+        lb::latent_attention_mma_kernel<256><<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
+    } else {
+        lb::latent_attention_mma_kernel<128><<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
+    }
     if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, 0, stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
     return LB_LAUNCH_RESULT();
 }

@@ -949,7 +949,7 @@ def latent_attention_tiling(num_heads: int) -> tuple[int, int]:
 def latent_attention_splits(num_items: int, num_heads: int, latent: int, window: int | None, max_context: int, sms: int | None = None) -> int:
     """Over how many CTAs an item's cached rows are shared out: 1 where the items fill the GPU by themselves."""
     heads, tokens = latent_attention_tiling(num_heads)
-    ctas = num_items * -(-num_heads // heads) * -(-latent // 128)
+    ctas = num_items * -(-num_heads // heads) * -(-latent // (256 if latent > 128 else 128))
     sms = sms or sm_count()
     rows = min(window, max_context) if window else max_context
     blocks = -(-(rows + tokens) // 64) + 1
