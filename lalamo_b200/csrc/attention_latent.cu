@@ -30,7 +30,7 @@ __device__ __forceinline__ T* latent_row(T* pages, const int* block_table, const
     return pages + row * (layout.latent + layout.rope);
 }
 
-// One block per token.
+// grid (tokens, heads + 1): block (t, h) lays out query head h of token t, block (t, heads) writes the token's row.
 //   q        [tokens][q_stride]: head h at h * (head_dim + rope), its last `rope` channels are rotated
 //   q_latent [heads][tokens][latent]: the heads' unrotated parts taken into the latent's space
 //   down     [tokens][down_stride]: [latent | rope]
@@ -48,43 +48,41 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q, int q_stride, con
     float* cosines = shared;            // half
     float* sines = shared + half;       // half
     float* scratch = sines + half;      // 33
-    const int token = blockIdx.x;
+    const int token = blockIdx.x, unit = blockIdx.y;
+    if (unit == num_heads && !write_kv) return;
     const int position = positions[token];
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(static_cast<float>(position) * inv_freq[i], &sines[i], &cosines[i]);
-    const T* row = down + static_cast<size_t>(token) * down_stride;
-    float squares = 0.0f;
-    if (write_kv) {
-        for (int d = threadIdx.x; d < latent; d += blockDim.x) {
-            const float v = to_float(row[d]);
-            squares += v * v;
-        }
-    }
-    const float total = block_sum(squares, scratch);   // also orders the writes to cosines[] and sines[]
-    if (write_kv) {
-        T* dst = latent_row(pages, block_table, layout, token_segment[token], position);
-        if (dst == nullptr) {
-            if (threadIdx.x == 0) report_error(status, kBadPage);
-        } else {
-            const float inv = rsqrtf(total / static_cast<float>(latent) + eps);
-            for (int d = threadIdx.x; d < latent; d += blockDim.x) dst[d] = from_float<T>(to_float(row[d]) * inv * (norm_weight[d] + scale_offset));
-            for (int i = threadIdx.x; i < half; i += blockDim.x) {
-                const float u = to_float(row[latent + i]), v = to_float(row[latent + half + i]);
-                dst[latent + i] = from_float<T>(u * cosines[i] - v * sines[i]);
-                dst[latent + half + i] = from_float<T>(v * cosines[i] + u * sines[i]);
-            }
-        }
-    }
-    const int full = latent + rope;
-    for (int head = 0; head < num_heads; ++head) {
-        const T* q_head = q + static_cast<size_t>(token) * q_stride + static_cast<size_t>(head) * (head_dim + rope) + head_dim;
-        const T* from = q_latent + (static_cast<size_t>(head) * tokens + token) * latent;
-        T* to = q_out + (static_cast<size_t>(token) * num_heads + head) * full;
+    if (unit < num_heads) {
+        __syncthreads();
+        const T* q_head = q + static_cast<size_t>(token) * q_stride + static_cast<size_t>(unit) * (head_dim + rope) + head_dim;
+        const T* from = q_latent + (static_cast<size_t>(unit) * tokens + token) * latent;
+        T* to = q_out + (static_cast<size_t>(token) * num_heads + unit) * (latent + rope);
         for (int d = threadIdx.x; d < latent; d += blockDim.x) to[d] = from[d];
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             const float u = to_float(q_head[i]), v = to_float(q_head[half + i]);
             to[latent + i] = from_float<T>(u * cosines[i] - v * sines[i]);
             to[latent + half + i] = from_float<T>(v * cosines[i] + u * sines[i]);
         }
+        return;
+    }
+    const T* row = down + static_cast<size_t>(token) * down_stride;
+    float squares = 0.0f;
+    for (int d = threadIdx.x; d < latent; d += blockDim.x) {
+        const float v = to_float(row[d]);
+        squares += v * v;
+    }
+    const float total = block_sum(squares, scratch);   // also orders the writes to cosines[] and sines[]
+    T* dst = latent_row(pages, block_table, layout, token_segment[token], position);
+    if (dst == nullptr) {
+        if (threadIdx.x == 0) report_error(status, kBadPage);
+        return;
+    }
+    const float inv = rsqrtf(total / static_cast<float>(latent) + eps);
+    for (int d = threadIdx.x; d < latent; d += blockDim.x) dst[d] = from_float<T>(to_float(row[d]) * inv * (norm_weight[d] + scale_offset));
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float u = to_float(row[latent + i]), v = to_float(row[latent + half + i]);
+        dst[latent + i] = from_float<T>(u * cosines[i] - v * sines[i]);
+        dst[latent + half + i] = from_float<T>(v * cosines[i] + u * sines[i]);
     }
 }
 
@@ -471,25 +469,36 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     }
 }
 
-// out[token][head] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits, in split order.  One block per (token, head).
+// out[token][head] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s over the splits, in split order.  One block per (token, head);
+// shared memory: a float per split.
 __global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int latent) {
+    extern __shared__ float split_weight[];
     const size_t row = blockIdx.x;
     const float* mine = partial + row * splits * (latent + 2);
-    float top = -INFINITY;
-    for (int s = 0; s < splits; ++s) top = fmaxf(top, mine[s * (latent + 2) + latent]);
-    float total = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = mine[s * (latent + 2) + latent];
-        if (m != -INFINITY) total += exp2f(m - top) * mine[s * (latent + 2) + latent + 1];
+    if (threadIdx.x < 32) {
+        float top = -INFINITY;
+        for (int s = threadIdx.x; s < splits; s += 32) top = fmaxf(top, mine[s * (latent + 2) + latent]);
+        top = warp_max(top);
+        for (int s = threadIdx.x; s < splits; s += 32) {
+            const float m = mine[s * (latent + 2) + latent];
+            split_weight[s] = m == -INFINITY ? 0.0f : exp2f(m - top);
+        }
+        __syncwarp();
+        if (threadIdx.x == 0) {
+            float total = 0.0f;
+            for (int s = 0; s < splits; ++s) total += split_weight[s] * mine[s * (latent + 2) + latent + 1];   // in split order
+            const float norm = total > 0.0f ? 1.0f / total : 0.0f;
+            for (int s = 0; s < splits; ++s) split_weight[s] *= norm;
+        }
     }
-    const float norm = total > 0.0f ? 1.0f / total : 0.0f;
+    __syncthreads();
     for (int d = threadIdx.x; d < latent; d += blockDim.x) {
         float sum = 0.0f;
         for (int s = 0; s < splits; ++s) {
-            const float m = mine[s * (latent + 2) + latent];
-            if (m != -INFINITY) sum += exp2f(m - top) * mine[s * (latent + 2) + d];
+            const float w = split_weight[s];
+            if (w != 0.0f) sum += w * mine[s * (latent + 2) + d];
         }
-        out[row * latent + d] = __float2bfloat16_rn(sum * norm);
+        out[row * latent + d] = __float2bfloat16_rn(sum);
     }
 }
 
@@ -507,7 +516,7 @@ int lb_latent_prepare(const void* q, int q_stride, const void* q_latent, const v
     const size_t shared = (static_cast<size_t>(rope) + 33) * sizeof(float);
     if (shared > 48 * 1024) return -2;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::latent_prepare_kernel<T><<<tokens, 128, shared, stream>>>(
+        lb::latent_prepare_kernel<T><<<dim3(tokens, num_heads + 1), 64, shared, stream>>>(
             static_cast<const T*>(q), q_stride, static_cast<const T*>(q_latent), static_cast<const T*>(down), down_stride, static_cast<T*>(q_out),
             static_cast<T*>(pages), norm_weight, eps, scale_offset, inv_freq, positions, token_segment, block_table, layout, tokens, num_heads, head_dim,
             write_kv, status);
@@ -576,7 +585,7 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
     } else {
         lb::latent_attention_mma_kernel<128><<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
     }
-    if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, 0, stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
+    if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, splits * sizeof(float), stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
     return LB_LAUNCH_RESULT();
 }
 

@@ -19,7 +19,8 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
     }
 }
 
-// One warp per token.
+// One warp per token or, with `block_per_token`, one block per token whose warps share out the experts' logits (few
+// tokens: more loads on their way at once), the first warp choosing afterwards.  A logit's sum is the same either way.
 //   z[e] = x . router[e] (+ bias[e])  (32-bit);   s[e] = sigmoid(z[e])   (score_kind 0),  softmax(z)[e]   (score_kind 1)  or  z[e]  (score_kind 2)
 //   experts form `group_count` equal groups of neighbours; a group's score is the sum of its two largest s (of its
 //   only one, in groups of one); experts outside the best `group_keep` groups cannot be chosen;
@@ -29,22 +30,28 @@ __device__ __forceinline__ void warp_argmax(float& value, int& index) {
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, int* __restrict__ chosen, float* __restrict__ weights,
                                  int tokens, int width, int experts, int top, int group_count, int group_keep, int score_kind, int renormalize,
-                                 float weight_scale, int row_floats, int group_floats, const float* __restrict__ bias) {
+                                 float weight_scale, int row_floats, int group_floats, const float* __restrict__ bias, int block_per_token) {
     extern __shared__ __align__(16) float shared[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int token = blockIdx.x * warps + warp;
+    const int token = block_per_token ? blockIdx.x : blockIdx.x * warps + warp;
     if (token >= tokens) return;
-    float* scores = shared + static_cast<size_t>(warp) * (2 * experts + group_floats + row_floats);   // a multiple of 4 floats per warp
+    const int sharers = block_per_token ? warps : 1, share = block_per_token ? warp : 0;   // the logits of experts 4 (share + i sharers) .. + 3 are this warp's
+    float* scores = shared + static_cast<size_t>(block_per_token ? 0 : warp) * (2 * experts + group_floats + row_floats);   // a multiple of 4 floats per warp
     float* candidates = scores + experts;
     float* group_score = candidates + experts;   // group_floats >= group_count of them
     float* x_s = group_score + group_floats;   // row_floats = width (rounded up to a multiple of 4) if the row is staged, else 0
     const T* row = x + static_cast<size_t>(token) * width;
     if (row_floats > 0) {
         // the token's row once into shared memory (32-bit), then four experts' rows at a time, 16 bytes a lane and turn
+        if (block_per_token) {
+            for (int d = threadIdx.x; d < width; d += blockDim.x) x_s[d] = to_float(row[d]);
+            __syncthreads();
+        } else {
 #pragma unroll 8
-        for (int d = lane; d < width; d += 32) x_s[d] = to_float(row[d]);
-        __syncwarp();
-        for (int e0 = 0; e0 < experts; e0 += 4) {
+            for (int d = lane; d < width; d += 32) x_s[d] = to_float(row[d]);
+            __syncwarp();
+        }
+        for (int e0 = 4 * share; e0 < experts; e0 += 4 * sharers) {
             float dots[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
             for (int c = 4 * lane; c < width; c += 128) {   // sixteen loads of the router's rows on their way at a time
@@ -65,13 +72,17 @@ __global__ void moe_route_kernel(const T* __restrict__ x, const float* __restric
             }
         }
     } else {
-        for (int e = 0; e < experts; ++e) {
+        for (int e = share; e < experts; e += sharers) {
             const float* w = router + static_cast<size_t>(e) * width;
             float dot = 0.0f;
             for (int d = lane; d < width; d += 32) dot += to_float(row[d]) * w[d];
             dot = warp_sum(dot);
             if (lane == 0) scores[e] = dot;
         }
+    }
+    if (block_per_token) {
+        __syncthreads();
+        if (warp != 0) return;
     }
     __syncwarp();
     if (bias != nullptr) {
@@ -524,13 +535,14 @@ int lb_moe_route(const void* x, const float* router, int* chosen, float* weights
     int row_floats = width % 4 == 0 ? width : 0;   // rows of 16-byte multiples are staged and read 16 bytes a lane
     if (static_cast<size_t>(kWarps) * (scratch + row_floats) * sizeof(float) > 160 * 1024) row_floats = 0;
     const size_t shared = static_cast<size_t>(kWarps) * (scratch + row_floats) * sizeof(float);
+    const int block_per_token = tokens <= 512 ? 1 : 0;   // few tokens: a block's warps share out a token's experts
     const int padded_groups = scratch - 2 * experts;   // the kernel lays the three arrays out by these counts
     LB_DISPATCH_DTYPE(dtype, {
         auto kernel = lb::moe_route_kernel<T>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-        kernel<<<(tokens + kWarps - 1) / kWarps, 32 * kWarps, shared, stream>>>(
+        kernel<<<block_per_token ? tokens : (tokens + kWarps - 1) / kWarps, 32 * kWarps, shared, stream>>>(
             static_cast<const T*>(x), router, chosen, weights, tokens, width, experts, top, group_count, group_keep, score_kind, renormalize, weight_scale,
-            row_floats, padded_groups, bias);
+            row_floats, padded_groups, bias, block_per_token);
     })
     return LB_LAUNCH_RESULT();
 }
