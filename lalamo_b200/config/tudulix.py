@@ -128,7 +128,6 @@ class TudulixConfig:
         heads = _positive(mixer, "heads", at)
         window = _positive(mixer, "mask.size", at)
         scale = _number(mixer, "scale", at)
-        base = _number(mixer, "rot.base", at)
         if kind == "attention":
             groups, dim = _positive(mixer, "kv_heads", at), _positive(mixer, "dim", at)
             if heads % groups:
@@ -141,7 +140,7 @@ class TudulixConfig:
                 num_heads=heads,
                 num_groups=groups,
                 head_dim=dim,
-                position=RopeSpec(rotary_dim=rot_dims, theta=base, pairing="interleaved") if rot_dims else None,
+                position=RopeSpec(rotary_dim=rot_dims, theta=_number(mixer, "rot.base", at), pairing="interleaved") if rot_dims else None,
                 window=window,
                 scale=scale,
                 value_dim=_positive(mixer, "vdim", at),
@@ -162,7 +161,7 @@ class TudulixConfig:
                 value_dim=_positive(mixer, "vdim", at),
                 latent_dim=rank,
                 latent_norm=RMSNormSpec(dim=rank, eps=eps, exact=True),
-                position=RopeSpec(rotary_dim=rot_dim, theta=base, pairing="half"),
+                position=RopeSpec(rotary_dim=rot_dim, theta=_number(mixer, "rot.base", at), pairing="half"),
                 window=window,
                 scale=scale,
                 gated=True,

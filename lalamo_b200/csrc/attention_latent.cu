@@ -323,6 +323,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     const int position_b = position0 + (row_b < rows_used ? row_b / heads_here : 0);
     const int first_a = p.window > 0 ? max(0, position_a - p.window + 1) : 0;
     const int first_b = p.window > 0 ? max(0, position_b - p.window + 1) : 0;
+    const int last_first = p.window > 0 ? max(0, last_position - p.window + 1) : 0;   // the first row the item's last query sees
     float o[kLatentMmaChunk / 8][4];
 #pragma unroll
     for (int j = 0; j < kLatentMmaChunk / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
@@ -370,19 +371,25 @@ latent_attention_mma_kernel(LatentMmaParams p) {
                     }
                 }
             }
-            // masks, and the block's maxima per row
+            // masks (only in blocks that reach past the item's first query or before its last query's window), and the
+            // block's maxima per row
             const int key0 = block * kLatentMmaKeys;
             float block_max_a = -INFINITY, block_max_b = -INFINITY;
+            if (key0 + kLatentMmaKeys - 1 > position0 || key0 < last_first) {
+#pragma unroll
+                for (int j = 0; j < kLatentMmaKeys / 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int key = key0 + 8 * j + 2 * t + e;
+                        if (key < first_a || key > position_a) s[j][e] = -INFINITY;
+                        if (key < first_b || key > position_b) s[j][2 + e] = -INFINITY;
+                    }
+                }
+            }
 #pragma unroll
             for (int j = 0; j < kLatentMmaKeys / 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int key = key0 + 8 * j + 2 * t + e;
-                    if (key < first_a || key > position_a) s[j][e] = -INFINITY;
-                    if (key < first_b || key > position_b) s[j][2 + e] = -INFINITY;
-                    block_max_a = fmaxf(block_max_a, s[j][e]);
-                    block_max_b = fmaxf(block_max_b, s[j][2 + e]);
-                }
+                block_max_a = fmaxf(block_max_a, fmaxf(s[j][0], s[j][1]));
+                block_max_b = fmaxf(block_max_b, fmaxf(s[j][2], s[j][3]));
             }
             block_max_a = fmaxf(block_max_a, __shfl_xor_sync(0xffffffffu, block_max_a, 1));
             block_max_a = fmaxf(block_max_a, __shfl_xor_sync(0xffffffffu, block_max_a, 2));
@@ -409,12 +416,14 @@ latent_attention_mma_kernel(LatentMmaParams p) {
             }
             sum_a = sum_a * keep_a + add_a;
             sum_b = sum_b * keep_b + add_b;
+            if (__any_sync(0xffffffffu, keep_a != 1.0f || keep_b != 1.0f)) {   // no row's maximum moved: nothing to rescale
 #pragma unroll
-            for (int j = 0; j < kLatentMmaChunk / 8; ++j) {
-                o[j][0] *= keep_a;
-                o[j][1] *= keep_a;
-                o[j][2] *= keep_b;
-                o[j][3] *= keep_b;
+                for (int j = 0; j < kLatentMmaChunk / 8; ++j) {
+                    o[j][0] *= keep_a;
+                    o[j][1] *= keep_a;
+                    o[j][2] *= keep_b;
+                    o[j][3] *= keep_b;
+                }
             }
             const __nv_bfloat16* v_address = k_block + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + chunk0 + (lane >> 4) * 8;
 #pragma unroll
