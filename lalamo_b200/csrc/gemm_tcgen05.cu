@@ -33,10 +33,26 @@ struct TcParams {
     int epilogue;
     int hidden;         // kTcGated: W is [2 * hidden, k], rows [up ; gate]; out is [tokens, hidden]
     int activation;
+    float limit;        // of activation 3 (the limited sigmoid gate, see common.cuh)
     int bulk_store;     // the walking kernel writes its output by bulk tensor stores (rows of the output 16-byte aligned)
     int early_successor;   // the one-tile kernel lets the kernel after it start before it has finished
     int* status;
 };
+
+// The two sides of a gated epilogue: hidden = tc_up_side(up) * tc_gate_side(gate).  Activations 0 to 2 are act(gate) * up;
+// activation 3 is min(gate, limit) * sigmoid(1.702 min(gate, limit)) * (clamp(up, -limit, limit) + 1).
+__device__ __forceinline__ float tc_gate_side(float g, int activation, float limit, bool fast) {
+    if (activation == kSigmoidLimit) {
+        const float c = fminf(g, limit);
+        return fast ? __fdividef(c, 1.0f + __expf(-kSigmoidLimitSlope * c)) : c / (1.0f + expf(-kSigmoidLimitSlope * c));
+    }
+    if (activation == 0) return fast ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + expf(-g));
+    if (activation == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f));
+    return g;
+}
+__device__ __forceinline__ float tc_up_side(float u, int activation, float limit) {
+    return activation == kSigmoidLimit ? fminf(fmaxf(u, -limit), limit) + 1.0f : u;
+}
 
 template <int BN, int STAGES>
 struct TcShared {
@@ -196,8 +212,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float g = __bfloat162float(gate[i]);
-                        const float act = p.activation == 0 ? g / (1.0f + expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
-                        result[i] = __float2bfloat16_rn(__bfloat162float(up[i]) * __bfloat162float(__float2bfloat16_rn(act)));
+                        const float act = tc_gate_side(g, p.activation, p.limit, false);
+                        result[i] = __float2bfloat16_rn(tc_up_side(__bfloat162float(up[i]), p.activation, p.limit) * __bfloat162float(__float2bfloat16_rn(act)));
                     }
                     __nv_bfloat16* destination = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(token) * p.hidden + row0 + part * 8;
                     if (p.hidden % 8 == 0 && row0 + kTcRows / 2 <= p.hidden) {
@@ -526,7 +542,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
 #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
                                     const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[piece * 8 + 2 * i + e])));
-                                    act[e] = p.activation == 0 ? __fdividef(g, 1.0f + __expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                                    act[e] = tc_gate_side(g, p.activation, p.limit, true);
                                 }
                                 halves[i] = __floats2bfloat162_rn(act[0], act[1]);
                             }
@@ -546,8 +562,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                                 const int token = piece * 8 + 2 * i;
                                 const float up0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token])));
                                 const float up1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token + 1])));
-                                stage[token * (kTcRows / 2)] = __float2bfloat16_rn(up0 * act.x);
-                                stage[(token + 1) * (kTcRows / 2)] = __float2bfloat16_rn(up1 * act.y);
+                                stage[token * (kTcRows / 2)] = __float2bfloat16_rn(tc_up_side(up0, p.activation, p.limit) * act.x);
+                                stage[(token + 1) * (kTcRows / 2)] = __float2bfloat16_rn(tc_up_side(up1, p.activation, p.limit) * act.y);
                             }
                         }
                     }
@@ -586,7 +602,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                                     const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[piece * 8 + 2 * i + e])));
                                     // exp and the division by fast hardware approximations (a few units in the
                                     // last place of float32, far below the bfloat16 rounding that follows)
-                                    act[e] = p.activation == 0 ? __fdividef(g, 1.0f + __expf(-g)) : p.activation == 1 ? 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) : g;
+                                    act[e] = tc_gate_side(g, p.activation, p.limit, true);
                                 }
                                 halves[i] = __floats2bfloat162_rn(act[0], act[1]);
                             }
@@ -609,8 +625,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
                                     const int token = piece * 8 + 2 * i;
                                     const float up0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token])));
                                     const float up1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[token + 1])));
-                                    if (whole || token < tokens_here) destination[static_cast<size_t>(token) * p.hidden] = __float2bfloat16_rn(up0 * act.x);
-                                    if (whole || token + 1 < tokens_here) destination[static_cast<size_t>(token + 1) * p.hidden] = __float2bfloat16_rn(up1 * act.y);
+                                    if (whole || token < tokens_here)
+                                        destination[static_cast<size_t>(token) * p.hidden] = __float2bfloat16_rn(tc_up_side(up0, p.activation, p.limit) * act.x);
+                                    if (whole || token + 1 < tokens_here)
+                                        destination[static_cast<size_t>(token + 1) * p.hidden] = __float2bfloat16_rn(tc_up_side(up1, p.activation, p.limit) * act.y);
                                 }
                             }
                         }
@@ -857,7 +875,7 @@ long long lb_gemm_tcgen05_scratch_floats(int tokens, int n, int slices) {
 // defer_sum: with more than one slice, leave the partial sums in `scratch` ([slices][tokens][n]) for the
 // caller (lb_sum_slices, or a consumer that adds them itself); `out` is not touched then.
 int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, long long scratch_floats, int tokens, int k, int n, int epilogue,
-                    int activation, int slices, int defer_sum, int* status, cudaStream_t stream) {
+                    int activation, int slices, int defer_sum, int* status, cudaStream_t stream, float limit) {
     if (tokens < 1 || n < 1 || k < 8 || k % 8 != 0 || epilogue < 0 || epilogue == 3 || epilogue > 4) return -2;
     if (epilogue == lb::kTcGated) {
         if (n % 2 != 0) return -2;
@@ -875,6 +893,7 @@ int lb_gemm_tcgen05(const void* x, const void* w, void* out, float* scratch, lon
     p.status = status;
     p.hidden = n / 2;
     p.activation = activation;
+    p.limit = limit;
     p.bulk_store = 0;
     p.early_successor = tokens > 16 ? 1 : 0;
     if (slices > 1) {

@@ -1243,7 +1243,7 @@ def _settled_slices(slices: int, width: int) -> int:
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", residual: torch.Tensor | None = None,
                    slices: int | None = None, activation: str = "identity", status: torch.Tensor | None = None,
-                   defer_sum: bool = False) -> torch.Tensor | SlicedSum:
+                   defer_sum: bool = False, limit: float = 0.0) -> torch.Tensor | SlicedSum:
     """``x @ weight.T`` on the tcgen05 tensor cores.  ``epilogue``: ``"store"`` (bfloat16),
     ``"store_float"``, ``"residual_add"`` (into ``residual``, float32, which is returned) or ``"gated"``
     (``weight`` is ``[up ; gate]``, the result ``up * activation(gate)`` of half as many columns).
@@ -1288,7 +1288,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store
         scratch = _tc_scratch[index]
     code = _lib().lb_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _ptr(scratch), c_longlong(scratch.numel() if scratch is not None else 0),
                                   c_int(tokens), c_int(width), c_int(rows), c_int(_TC_EPILOGUES[epilogue]), c_int(_ACTIVATIONS[activation]), c_int(slices),
-                                  c_int(1 if deferred else 0), _ptr(status), _stream())
+                                  c_int(1 if deferred else 0), _ptr(status), _stream(), c_float(limit))
     if code == -5:
         raise KernelError("linear_tcgen05: the driver gave no tensor map (cuTensorMapEncodeTiled)")
     _done(code, "gemm_tcgen05", 2 if slices > 1 and not deferred else 1)
@@ -1365,15 +1365,14 @@ def gated_linear(x: torch.Tensor, up_gate: torch.Tensor, activation: str, status
     hidden = up_gate.shape[0] // 2
     if x.shape[-1] != up_gate.shape[1] or up_gate.shape[0] != 2 * hidden:
         raise KernelError("gated_linear: shapes of x and up_gate do not agree")
-    fused_on_tcgen05 = activation != "sigmoid_limit"   # the tcgen05 product's gated epilogue has the one-input activations only
-    if fused_on_tcgen05 and USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
-        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
+    if USE_TCGEN05 and x.shape[0] <= SKINNY_MAX_TOKENS and up_gate.shape[0] >= TCGEN05_MIN_ROWS_FEW_TOKENS and tcgen05_supported(x, up_gate.shape[0]):
+        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status, limit=limit)
     out = torch.empty(x.shape[0], hidden, dtype=x.dtype, device=x.device)
     if skinny_supported(x, hidden):
         _skinny(x, up_gate, out, hidden, "gated", activation, limit=limit)
         return out
-    if fused_on_tcgen05 and USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
-        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status)
+    if USE_TCGEN05 and tcgen05_supported(x, up_gate.shape[0]):
+        return linear_tcgen05(x, up_gate, "gated", activation=activation, status=status, limit=limit)
     fused = linear(x, up_gate, status=status)
     gated_activation(fused.sum() if isinstance(fused, SlicedSum) else fused, out, activation, limit)
     return out

@@ -363,9 +363,10 @@ def test_experts_with_the_limited_sigmoid_gate(tokens, width, ff, experts, top, 
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens,width,ff", [(3, 64, 40), (16, 128, 256), (17, 128, 256), (200, 256, 320), (40, 72, 28)])
+@pytest.mark.parametrize("tokens,width,ff", [(3, 64, 40), (16, 128, 256), (17, 128, 256), (100, 128, 72), (200, 256, 320), (40, 72, 28), (600, 512, 520), (2048, 256, 1152)])
 def test_dense_expert_with_the_limited_sigmoid_gate(tokens, width, ff, dtype):
-    """The shared expert through the feed-forward part: few tokens (the weight-streaming product's epilogue) and many."""
+    """The shared expert through the feed-forward part: few tokens (the weight-streaming product's epilogue), some (the one-tile
+    tcgen05 product's) and many (the walking product's, with and without bulk stores)."""
     from lalamo_b200.config.plan import GatedMLPSpec
     from lalamo_b200.parts.base import Runtime, build_part
 
