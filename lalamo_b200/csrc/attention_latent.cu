@@ -254,7 +254,7 @@ latent_attention_mma_kernel(LatentMmaParams p) {
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(latent_shared);          // [64][pitch]
     __nv_bfloat16* k_s = q_s + kLatentMmaRows * pitch;                             // [2][64][pitch]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int item = blockIdx.x;
+    const int item = gridDim.x - 1 - blockIdx.x;   // a prompt's last items see the most rows: they start first
     const int head_block = blockIdx.y / p.splits, split = blockIdx.y - head_block * p.splits;
     const int chunk0 = blockIdx.z * kLatentMmaChunk;
     const int chunk = min(kLatentMmaChunk, latent - chunk0);   // a multiple of 16
@@ -503,10 +503,8 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bflo
     __syncthreads();
     for (int d = threadIdx.x; d < latent; d += blockDim.x) {
         float sum = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float w = split_weight[s];
-            if (w != 0.0f) sum += w * mine[s * (latent + 2) + d];
-        }
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) sum += split_weight[s] * mine[s * (latent + 2) + d];   // a split that saw nothing left zeros
         out[row * latent + d] = __float2bfloat16_rn(sum);
     }
 }

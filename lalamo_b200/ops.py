@@ -1038,7 +1038,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, *, top: int, group_count: i
     return chosen, weights
 
 
-MOE_STREAM_MAX_PAIRS = 16  # up to this many (token, expert) pairs each pair streams its expert's weights; more are grouped by expert
+MOE_STREAM_MAX_PAIRS = 32  # up to this many (token, expert) pairs each pair streams its expert's weights; more are grouped by expert (measured: 24 pairs 30 % faster streamed, 48 pairs as fast either way)
 
 
 def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
