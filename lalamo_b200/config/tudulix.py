@@ -126,7 +126,7 @@ class TudulixConfig:
         mixer = _get(entry, "mixer", Mapping, where)
         at = where + ".mixer"
         heads = _positive(mixer, "heads", at)
-        window = _positive(mixer, "mask.size", at)
+        window = min(_positive(mixer, "mask.size", at), 1 << 30)   # wider than any context: the kernels count in 32 bits
         scale = _number(mixer, "scale", at)
         if kind == "attention":
             groups, dim = _positive(mixer, "kv_heads", at), _positive(mixer, "dim", at)
