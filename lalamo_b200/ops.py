@@ -955,7 +955,7 @@ def latent_attention_splits(num_items: int, num_heads: int, latent: int, window:
     blocks = -(-(rows + tokens) // 64) + 1
     if ctas >= 2 * sms or blocks <= 2:
         return 1
-    return max(1, min(blocks, -(-2 * sms // ctas), 32))
+    return max(1, min(blocks // 2, -(-2 * sms // ctas), 32))   # two blocks a CTA: one block each was measured 1 % slower
 
 
 def latent_attention(q: torch.Tensor, pages: torch.Tensor, out: torch.Tensor, *, items: torch.Tensor, num_items: int, positions: torch.Tensor,
