@@ -8,6 +8,7 @@
 //   latent_attention_plain   one block per (token, head): 32-bit scores, softmax and sums; the 32-bit path's
 //                            attention and the reference for the tensor-core kernel
 //   gate_heads               heads' values [head][token][vdim] times sigmoid(gate), laid out [token][head * vdim]
+//   heads_product            the two small products per head (queries into the latent's space, sums out of it, the latter with the gate)
 #include "common.cuh"
 
 namespace lb {
@@ -30,7 +31,7 @@ __device__ __forceinline__ T* latent_row(T* pages, const int* block_table, const
     return pages + row * (layout.latent + layout.rope);
 }
 
-// grid (tokens, heads + 1): block (t, h) lays out query head h of token t, block (t, heads) writes the token's row.
+// grid (tokens, head blocks + 1): blocks (t, b) lay out token t's query heads, block (t, head blocks) writes the token's row.
 //   q        [tokens][q_stride]: head h at h * (head_dim + rope), its last `rope` channels are rotated
 //   q_latent [heads][tokens][latent]: the heads' unrotated parts taken into the latent's space
 //   down     [tokens][down_stride]: [latent | rope]
@@ -48,20 +49,28 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q, int q_stride, con
     float* cosines = shared;            // half
     float* sines = shared + half;       // half
     float* scratch = sines + half;      // 33
-    const int token = blockIdx.x, unit = blockIdx.y;
-    if (unit == num_heads && !write_kv) return;
+    // blocks (t, 0 .. head_blocks - 1) take heads_per_block heads each (one where the latent parts are copied, all where only
+    // the rotated parts are written), block (t, head_blocks) the token's row
+    const int token = blockIdx.x, unit = blockIdx.y, head_blocks = gridDim.y - 1, heads_per_block = (num_heads + head_blocks - 1) / head_blocks;
+    if (unit == head_blocks && !write_kv) return;
     const int position = positions[token];
     for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(static_cast<float>(position) * inv_freq[i], &sines[i], &cosines[i]);
-    if (unit < num_heads) {
+    if (unit < head_blocks) {
         __syncthreads();
-        const T* q_head = q + static_cast<size_t>(token) * q_stride + static_cast<size_t>(unit) * (head_dim + rope) + head_dim;
-        const T* from = q_latent + (static_cast<size_t>(unit) * tokens + token) * latent;
-        T* to = q_out + (static_cast<size_t>(token) * num_heads + unit) * (latent + rope);
-        for (int d = threadIdx.x; d < latent; d += blockDim.x) to[d] = from[d];
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const int head0 = unit * heads_per_block, heads_here = min(num_heads, head0 + heads_per_block) - head0;
+        if (q_latent != nullptr) {   // null: whoever made them wrote them into q_out already
+            for (int c = threadIdx.x; c < heads_here * latent; c += blockDim.x) {
+                const int head = head0 + c / latent, d = c % latent;
+                q_out[(static_cast<size_t>(token) * num_heads + head) * (latent + rope) + d] = q_latent[(static_cast<size_t>(head) * tokens + token) * latent + d];
+            }
+        }
+        for (int c = threadIdx.x; c < heads_here * half; c += blockDim.x) {   // every pair of every head at once: one trip to memory
+            const int head = head0 + c / half, i = c % half;
+            const T* q_head = q + static_cast<size_t>(token) * q_stride + static_cast<size_t>(head) * (head_dim + rope) + head_dim;
+            T* to = q_out + (static_cast<size_t>(token) * num_heads + head) * (latent + rope) + latent;
             const float u = to_float(q_head[i]), v = to_float(q_head[half + i]);
-            to[latent + i] = from_float<T>(u * cosines[i] - v * sines[i]);
-            to[latent + half + i] = from_float<T>(v * cosines[i] + u * sines[i]);
+            to[i] = from_float<T>(u * cosines[i] - v * sines[i]);
+            to[half + i] = from_float<T>(v * cosines[i] + u * sines[i]);
         }
         return;
     }
@@ -509,6 +518,104 @@ __global__ void latent_merge_kernel(const float* __restrict__ partial, __nv_bflo
     }
 }
 
+
+// ------------------------------------------------------------------ one small product per head
+// out[t][h][n] = sum_k a[t][h][k] * B_h[k][n] for every head h, with B_h stored [K][N] (B_KN: a head's key projection, which takes
+// the unrotated query channels into the latent's space) or [N][K] (a head's value projection applied to the summed rows), optionally
+// times sigmoid(gate[t][h][n]).  Rows of a, out and gate are addressed by a token stride and a head stride, so inputs may be column
+// slices of a wider product and the output a part of wider rows.  grid (blocks of 64 tokens, heads, blocks of 64 columns), four warps
+// of 16 tokens; the tokens' rows and the columns' part of the head's matrix lie in shared memory; bfloat16, mma.sync with 32-bit sums;
+// K and N multiples of 16.
+struct HeadsProductParams {
+    const __nv_bfloat16* a;
+    long long a_token_stride;
+    int a_head_stride;
+    const __nv_bfloat16* b;
+    __nv_bfloat16* out;
+    long long out_token_stride;
+    int out_head_stride;
+    const __nv_bfloat16* gate;   // or null
+    long long gate_token_stride;
+    int gate_head_stride;
+    int tokens, k, n;
+    int blocks_per_cta;   // blocks of 64 columns a CTA takes
+};
+
+template <bool B_KN>
+__global__ void __launch_bounds__(128)
+heads_product_kernel(HeadsProductParams p) {
+    extern __shared__ __align__(16) unsigned char product_shared[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, head = blockIdx.y, token0 = blockIdx.x * 64;
+    // grid.z shares out the blocks of 64 columns; a CTA takes blocks_per_cta neighbouring blocks, whose part of the head's matrix it loads at once
+    const int first_column = blockIdx.z * p.blocks_per_cta * 64, share = min(p.blocks_per_cta * 64, p.n - first_column);
+    const int a_pitch = p.k + 8, b_pitch = (B_KN ? p.blocks_per_cta * 64 : p.k) + 8;
+    __nv_bfloat16* a_s = reinterpret_cast<__nv_bfloat16*>(product_shared);   // [64][k + 8]
+    __nv_bfloat16* b_s = a_s + 64 * a_pitch;                                   // [k][share + 8] or [share][k + 8]
+    const int a_pieces = p.k / 8;
+    const int rows_here = min(64, p.tokens - token0);
+    for (int c = tid; c < rows_here * a_pieces; c += 128) {
+        const int r = c / a_pieces, piece = c - r * a_pieces;
+        latent_copy_16(a_s + r * a_pitch + piece * 8, p.a + static_cast<size_t>(token0 + r) * p.a_token_stride + static_cast<size_t>(head) * p.a_head_stride + piece * 8, true);
+    }
+    {
+        const int b_rows = B_KN ? p.k : share, b_pieces = (B_KN ? share : p.k) / 8, b_global_pitch = B_KN ? p.n : p.k;
+        const __nv_bfloat16* b_head = p.b + static_cast<size_t>(head) * p.k * p.n + (B_KN ? first_column : static_cast<size_t>(first_column) * p.k);
+        for (int c = tid; c < b_rows * b_pieces; c += 128) {
+            const int r = c / b_pieces, piece = c - r * b_pieces;
+            latent_copy_16(b_s + r * b_pitch + piece * 8, b_head + static_cast<size_t>(r) * b_global_pitch + piece * 8, true);
+        }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    if (warp * 16 >= rows_here) return;   // (rows past the tokens hold whatever shared memory held: their results are not stored)
+    const int g = lane >> 2, t = lane & 3;
+    const __nv_bfloat16* a_address = a_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * a_pitch + (lane >> 4) * 8;
+    for (int local = 0; local < share; local += 64) {
+        const int n0 = first_column + local, columns = min(64, share - local);   // a multiple of 16
+        float acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+        for (int k0 = 0; k0 < p.k; k0 += 16) {
+            uint32_t a[4], b[4][4];
+            ldmatrix_x4(a, a_address + k0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (16 * j < columns) {
+                    if constexpr (B_KN) ldmatrix_x4_trans(b[j], b_s + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * b_pitch + local + j * 16 + (lane >> 4) * 8);
+                    else ldmatrix_x4(b[j], b_s + (local + j * 16 + (lane & 7) + (lane >> 4) * 8) * b_pitch + k0 + ((lane >> 3) & 1) * 8);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (16 * j < columns) {
+                    latent_mma(acc[2 * j], a, b[j][0], b[j][1]);
+                    latent_mma(acc[2 * j + 1], a, b[j][2], b[j][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int token = token0 + warp * 16 + g + 8 * half;
+            if (token >= p.tokens) continue;
+            __nv_bfloat16* dst = p.out + static_cast<size_t>(token) * p.out_token_stride + static_cast<size_t>(head) * p.out_head_stride + n0;
+            const __nv_bfloat16* gate = p.gate ? p.gate + static_cast<size_t>(token) * p.gate_token_stride + static_cast<size_t>(head) * p.gate_head_stride + n0 : nullptr;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (8 * j >= columns) continue;
+                float low = acc[j][2 * half], high = acc[j][2 * half + 1];
+                if (gate != nullptr) {
+                    const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + 8 * j + 2 * t));
+                    // the product is rounded as it would be stored, then gated
+                    low = __bfloat162float(__float2bfloat16_rn(low)) / (1.0f + expf(-z.x));
+                    high = __bfloat162float(__float2bfloat16_rn(high)) / (1.0f + expf(-z.y));
+                }
+                *reinterpret_cast<uint32_t*>(dst + 8 * j + 2 * t) = latent_pack(low, high);
+            }
+        }
+    }
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -523,7 +630,7 @@ int lb_latent_prepare(const void* q, int q_stride, const void* q_latent, const v
     const size_t shared = (static_cast<size_t>(rope) + 33) * sizeof(float);
     if (shared > 48 * 1024) return -2;
     LB_DISPATCH_DTYPE(dtype, {
-        lb::latent_prepare_kernel<T><<<dim3(tokens, num_heads + 1), 64, shared, stream>>>(
+        lb::latent_prepare_kernel<T><<<dim3(tokens, (q_latent != nullptr ? num_heads : 1) + 1), q_latent != nullptr ? 64 : 128, shared, stream>>>(
             static_cast<const T*>(q), q_stride, static_cast<const T*>(q_latent), static_cast<const T*>(down), down_stride, static_cast<T*>(q_out),
             static_cast<T*>(pages), norm_weight, eps, scale_offset, inv_freq, positions, token_segment, block_table, layout, tokens, num_heads, head_dim,
             write_kv, status);
@@ -593,6 +700,52 @@ int lb_latent_attention_mma(const void* q, const void* pages, void* out, float* 
         lb::latent_attention_mma_kernel<128><<<grid, lb::kLatentMmaThreads, shared, stream>>>(p);
     }
     if (splits > 1) lb::latent_merge_kernel<<<tokens * num_heads, 128, splits * sizeof(float), stream>>>(partial, static_cast<__nv_bfloat16*>(out), splits, latent);
+    return LB_LAUNCH_RESULT();
+}
+
+// a [tokens][heads][k], out [tokens][heads][n] and gate (or null) addressed by (token stride, head stride) in elements; b [heads][k][n]
+// if b_is_kn, else [heads][n][k].  bfloat16; k and n multiples of 16; every row 16-byte aligned (gate: 4-byte).  -2 otherwise.
+int lb_heads_product(const void* a, long long a_token_stride, int a_head_stride, const void* b, int b_is_kn, void* out, long long out_token_stride,
+                     int out_head_stride, const void* gate, long long gate_token_stride, int gate_head_stride, int tokens, int heads, int k, int n,
+                     cudaStream_t stream) {
+    if (tokens == 0 || heads == 0) return 0;
+    if (k < 16 || n < 16 || k % 16 != 0 || n % 16 != 0 || a_token_stride % 8 != 0 || a_head_stride % 8 != 0 || out_token_stride % 2 != 0 ||
+        out_head_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 4 != 0 ||
+        (gate != nullptr && (gate_token_stride % 2 != 0 || gate_head_stride % 2 != 0 || reinterpret_cast<uintptr_t>(gate) % 4 != 0)))
+        return -2;
+    // blocks of 64 columns are shared out over grid.z as far as that is needed to fill the GPU, and to fit a CTA's share into shared memory
+    const int token_blocks = (tokens + 63) / 64, column_blocks = (n + 63) / 64;
+    int shares = (2 * lb::multiprocessor_count() + token_blocks * heads - 1) / (token_blocks * heads);
+    shares = shares < 1 ? 1 : (shares > column_blocks ? column_blocks : shares);
+    int blocks_per_cta = (column_blocks + shares - 1) / shares;
+    auto shared_bytes = [&](int blocks) {
+        return (static_cast<size_t>(64) * (k + 8) + (b_is_kn ? static_cast<size_t>(k) * (blocks * 64 + 8) : static_cast<size_t>(blocks) * 64 * (k + 8))) * sizeof(__nv_bfloat16);
+    };
+    while (blocks_per_cta > 1 && shared_bytes(blocks_per_cta) > 100 * 1024) --blocks_per_cta;   // two CTAs an SM at least
+    const size_t shared = shared_bytes(blocks_per_cta);
+    if (shared > 227 * 1024) return -2;
+    static lb::OncePerDevice once_kn, once_nk;
+    const cudaError_t allowed = b_is_kn ? lb::allow_shared_memory(once_kn, lb::heads_product_kernel<true>, 227 * 1024)
+                                        : lb::allow_shared_memory(once_nk, lb::heads_product_kernel<false>, 227 * 1024);
+    if (allowed != cudaSuccess) return static_cast<int>(allowed);
+    lb::HeadsProductParams p;
+    p.a = static_cast<const __nv_bfloat16*>(a);
+    p.a_token_stride = a_token_stride;
+    p.a_head_stride = a_head_stride;
+    p.b = static_cast<const __nv_bfloat16*>(b);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.out_token_stride = out_token_stride;
+    p.out_head_stride = out_head_stride;
+    p.gate = static_cast<const __nv_bfloat16*>(gate);
+    p.gate_token_stride = gate_token_stride;
+    p.gate_head_stride = gate_head_stride;
+    p.tokens = tokens;
+    p.k = k;
+    p.n = n;
+    p.blocks_per_cta = blocks_per_cta;
+    const dim3 grid(token_blocks, heads, (column_blocks + blocks_per_cta - 1) / blocks_per_cta);
+    if (b_is_kn) lb::heads_product_kernel<true><<<grid, 128, shared, stream>>>(p);
+    else lb::heads_product_kernel<false><<<grid, 128, shared, stream>>>(p);
     return LB_LAUNCH_RESULT();
 }
 

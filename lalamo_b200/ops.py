@@ -870,6 +870,29 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, transpose_weight: bool =
     return torch.bmm(x, weight.transpose(1, 2) if transpose_weight else weight)
 
 
+def heads_product_supported(dtype: torch.dtype, k: int, n: int) -> bool:
+    """Whether :func:`heads_product` (the framework's own kernel) takes a per-head product of these sizes."""
+    return dtype == torch.bfloat16 and k >= 16 and n >= 16 and k % 16 == 0 and n % 16 == 0 and (64 * (k + 8) + max(k * 72, 64 * (k + 8))) * 2 <= 227 * 1024
+
+
+def heads_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, *, weight_is_kn: bool, gate: torch.Tensor | None = None) -> None:
+    """``out[t, h] = x[t, h] @ weight[h]`` (``weight [heads, k, n]``, ``weight_is_kn``) or ``x[t, h] @ weight[h].T`` (``weight [heads, n, k]``),
+    optionally times ``sigmoid(gate[t, h])``; bfloat16 on the tensor cores with 32-bit sums.  ``x [tokens, heads, k]``, ``out`` and ``gate``
+    ``[tokens, heads, n]`` may be views with any token and head strides (column slices of wider products, parts of wider rows)."""
+    _check(weight, "weight", torch.bfloat16)
+    tokens, heads, k = x.shape
+    n = weight.shape[2] if weight_is_kn else weight.shape[1]
+    if weight.shape != ((heads, k, n) if weight_is_kn else (heads, n, k)) or out.shape != (tokens, heads, n) or not heads_product_supported(x.dtype, k, n):
+        raise KernelError(f"heads_product: x {tuple(x.shape)}, weight {tuple(weight.shape)} and out {tuple(out.shape)} are not shapes the kernel takes")
+    for name, tensor in (("x", x), ("out", out), ("gate", gate)):
+        if tensor is not None and (not tensor.is_cuda or tensor.dtype != torch.bfloat16 or tensor.stride(2) != 1 or (name == "gate" and tensor.shape != out.shape)):
+            raise KernelError(f"heads_product: {name} must be a bfloat16 CUDA tensor [tokens, heads, .] with unit stride along the last dimension")
+    code = _lib().lb_heads_product(_ptr(x), c_longlong(x.stride(0)), c_int(x.stride(1)), _ptr(weight), c_int(1 if weight_is_kn else 0), _ptr(out),
+                                   c_longlong(out.stride(0)), c_int(out.stride(1)), _ptr(gate), c_longlong(gate.stride(0) if gate is not None else 0),
+                                   c_int(gate.stride(1) if gate is not None else 0), c_int(tokens), c_int(heads), c_int(k), c_int(n), _stream())
+    _done(code, "heads_product")
+
+
 def _check_latent_pages(pages: torch.Tensor, block_table: torch.Tensor, latent: int, rope: int) -> tuple[int, int, int]:
     _check(pages, "pages")
     _check(block_table, "block_table", torch.int32)
@@ -880,25 +903,26 @@ def _check_latent_pages(pages: torch.Tensor, block_table: torch.Tensor, latent: 
     return pages.shape[1], pages.shape[0], block_table.shape[1]
 
 
-def latent_prepare(q: torch.Tensor, q_latent: torch.Tensor, down: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *, norm_weight: torch.Tensor,
+def latent_prepare(q: torch.Tensor, q_latent: torch.Tensor | None, down: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *, norm_weight: torch.Tensor,
                    eps: float, scale_offset: float, inv_freq: torch.Tensor, positions: torch.Tensor, token_segment: torch.Tensor,
                    block_table: torch.Tensor, num_heads: int, head_dim: int, latent: int, rope: int, write_kv: bool, status: torch.Tensor) -> None:
     """Latent attention's step between the projections and the attention.  ``q [tokens, heads * (head_dim + rope)]`` and
     ``down [tokens, latent + rope]`` may be column slices of a wider product (row strides are passed on).  Writes the
     row ``[norm(down[:latent]) * (norm_weight + scale_offset) | rope(down[latent:])]`` into the token's page and the
-    queries ``[q_latent[h, t] | rope(q[t, h, head_dim:])]`` into ``q_out [tokens, heads, latent + rope]``; the rotation
-    pairs channel ``i`` with ``i + rope / 2``."""
+    queries ``[q_latent[h, t] | rope(q[t, h, head_dim:])]`` into ``q_out [tokens, heads, latent + rope]`` (``q_latent=None``:
+    the latent parts are in ``q_out`` already and stay); the rotation pairs channel ``i`` with ``i + rope / 2``."""
     tokens = q_out.shape[0]
     for name, tensor in (("q", q), ("down", down)):
         if not tensor.is_cuda or tensor.dim() != 2 or tensor.stride(1) != 1 or tensor.dtype != q_out.dtype or tensor.shape[0] != tokens:
             raise KernelError(f"latent_prepare: {name} must be a [tokens, .] CUDA tensor of q_out's type with unit column stride")
-    _check(q_latent, "q_latent", q_out.dtype)
+    if q_latent is not None:
+        _check(q_latent, "q_latent", q_out.dtype)
     _check(q_out, "q_out")
     _check(norm_weight, "norm_weight", torch.float32)
     _check(inv_freq, "inv_freq", torch.float32)
     _check(positions, "positions", torch.int32)
     _check(token_segment, "token_segment", torch.int32)
-    if (q.shape[1] != num_heads * (head_dim + rope) or down.shape[1] != latent + rope or q_latent.shape != (num_heads, tokens, latent)
+    if (q.shape[1] != num_heads * (head_dim + rope) or down.shape[1] != latent + rope or (q_latent is not None and q_latent.shape != (num_heads, tokens, latent))
             or q_out.shape != (tokens, num_heads, latent + rope) or norm_weight.numel() != latent or inv_freq.numel() != rope // 2 or rope % 2):
         raise KernelError("latent_prepare: the sizes of q, q_latent, down, q_out, the norm's weight and the frequencies do not agree")
     page_size, num_pages, max_blocks = _check_latent_pages(pages, block_table, latent, rope)

@@ -87,10 +87,17 @@ class LatentAttention(Mixer):
         q = projected[:, : self.q_width]
         gate = projected[:, self.q_width : self.q_width + self.gate_width] if spec.gated else None
         down = projected[:, self.q_width + self.gate_width :]
-        # the heads' unrotated query parts into the latent's space: [head][token][latent]
-        q_plain = q.view(tokens, heads, dim + rope)[:, :, :dim].transpose(0, 1)
-        q_latent = ops.heads_linear(q_plain, self.key_up)
         queries = runtime.empty(tokens, heads, latent + rope)
+        per_head = q.view(tokens, heads, dim + rope)
+        # the heads' unrotated query parts into the latent's space: the framework's own kernel writes them where the attention
+        # reads them; sizes it does not take (and the 32-bit path) go through a batched library product, [head][token][latent]
+        own_products = ops.heads_product_supported(runtime.dtype, dim, latent) and ops.heads_product_supported(runtime.dtype, latent, spec.value_dim) \
+            and projected.shape[1] % 8 == 0 and (dim + rope) % 8 == 0 and self.q_width % 2 == 0
+        q_latent = None
+        if own_products:
+            ops.heads_product(per_head[:, :, :dim], self.key_up, queries[:, :, :latent], weight_is_kn=True)
+        else:
+            q_latent = ops.heads_linear(per_head[:, :, :dim].transpose(0, 1), self.key_up)
         ops.latent_prepare(q, q_latent, down, queries, cache.k_pages, norm_weight=self.latent_norm, eps=spec.latent_norm.eps,
                            scale_offset=spec.latent_norm.scale_offset, inv_freq=self.position.inv_freq, positions=step.positions,
                            token_segment=step.token_segment, block_table=cache.block_table, num_heads=heads, head_dim=dim, latent=latent, rope=rope,
@@ -105,9 +112,14 @@ class LatentAttention(Mixer):
             ops.latent_attention(queries, cache.k_pages, summed, items=lists["items"], num_items=num_items, splits=splits, **common)
         else:
             ops.latent_attention_plain(queries, cache.k_pages, summed, **common)
-        values = ops.heads_linear(summed.transpose(0, 1), self.value_up, transpose_weight=True)   # [head][token][vdim]
         mixed = runtime.empty(tokens, heads * spec.value_dim)
-        ops.gate_heads(values, gate, mixed)
+        if own_products:
+            # the heads' value projections applied to the sums, times the gate, laid out for the out-projection
+            ops.heads_product(summed, self.value_up, mixed.view(tokens, heads, spec.value_dim), weight_is_kn=False,
+                              gate=gate.view(tokens, heads, spec.value_dim) if gate is not None else None)
+        else:
+            values = ops.heads_linear(summed.transpose(0, 1), self.value_up, transpose_weight=True)   # [head][token][vdim]
+            ops.gate_heads(values, gate, mixed)
         if residual is not None:
             return ops.linear_accumulate(mixed, self.out_proj, residual, status=runtime.status)
         return ops.linear(mixed, self.out_proj, status=runtime.status)

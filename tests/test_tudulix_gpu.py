@@ -548,3 +548,28 @@ def test_heads_products_and_the_gate(dtype):
     ops.gate_heads(got, gate[:, 3:], mixed)
     want = got.double().cpu().numpy().transpose(1, 0, 2).reshape(tokens, heads * n) * plain.sigmoid(gate[:, 3:].double().cpu().numpy())
     assert np.abs(mixed.float().cpu().numpy() - want).max() < (1e-5 if dtype == torch.float32 else 0.03)
+
+
+@pytest.mark.parametrize("tokens,heads,k,n", [(19, 3, 48, 80), (64, 2, 64, 256), (150, 5, 256, 64), (1, 16, 64, 128), (300, 1, 16, 16), (8, 4, 128, 512)])
+def test_heads_products_of_the_frameworks_own(tokens, heads, k, n):
+    """The per-head products on the framework's kernel: both orientations of the heads' matrices, inputs that are column slices of wider
+    rows, outputs that are parts of wider rows, the gate read from a slice; token counts that fill no block of 64."""
+    from lalamo_b200 import ops
+
+    generator = np.random.default_rng(tokens + k)
+    make = lambda *shape: torch.from_numpy(generator.standard_normal(shape)).to(torch.bfloat16).cuda()
+    wide = make(tokens, heads * (k + 8) + 24)   # heads of k + 8 channels of which the first k are used, then other columns
+    x = wide[:, : heads * (k + 8)].view(tokens, heads, k + 8)[:, :, :k]
+    w_kn = make(heads, k, n) / 4
+    out_wide = torch.full((tokens, heads, n + 16), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.heads_product(x, w_kn, out_wide[:, :, :n], weight_is_kn=True)
+    want = np.einsum("thk,hkn->thn", x.double().cpu().numpy(), w_kn.double().cpu().numpy())
+    assert np.abs(out_wide[:, :, :n].float().cpu().numpy() - want).max() < 0.02 * max(1.0, np.abs(want).max())
+    assert (out_wide[:, :, n:] == 7.0).all()   # the rest of the rows stays
+    w_nk = make(heads, n, k) / 4
+    gate_wide = make(tokens, 10 + heads * n)
+    gate = gate_wide[:, 10:].view(tokens, heads, n)
+    out = torch.empty(tokens, heads * n, dtype=torch.bfloat16, device="cuda")
+    ops.heads_product(x, w_nk, out.view(tokens, heads, n), weight_is_kn=False, gate=gate)
+    want = np.einsum("thk,hnk->thn", x.double().cpu().numpy(), w_nk.double().cpu().numpy()) * plain.sigmoid(gate.double().cpu().numpy())
+    assert np.abs(out.view(tokens, heads, n).float().cpu().numpy() - want).max() < 0.02 * max(1.0, np.abs(want).max())
