@@ -268,7 +268,8 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
 }
 
 // The norm of a sublayer's output, added to the residual stream.  One block per row r:
-//   y = scale_a * (a[r] + bias_a) + scale_b * (b[r] + bias_b)        (b and the biases may be absent)
+//   y = scale_a * (a[r] + bias_a) + scale_b * (b[r] + bias_b)        (b and the biases may be absent; a may be given as the
+//                                                                      un-summed outputs of a row's routed experts with their weights)
 //   residual[r] += y * rsqrt(mean(y^2) + eps) * (w + offset)
 //   rounded[r] = T(residual[r])                                      (if asked for: the next sublayer's input)
 //   or, with next_weight: rounded[r] = T(residual[r] * rsqrt(mean(residual[r]^2) + next_eps) * (next_weight + next_offset)),
@@ -278,7 +279,9 @@ template <typename T>
 __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ bias_a, float scale_a,
                                        const T* __restrict__ b, const float* __restrict__ bias_b, float scale_b,
                                        const float* __restrict__ weight, T* __restrict__ rounded, int dim, float eps, float scale_offset,
-                                       const float* __restrict__ next_weight, float next_eps, float next_offset) {
+                                       const float* __restrict__ next_weight, float next_eps, float next_offset,
+                                       const float* __restrict__ pair_out, const float* __restrict__ pair_weight, const int* __restrict__ pair_expert,
+                                       int top, int experts) {
     extern __shared__ float shared[];
     allow_next_kernel();   // as in cast_rows_kernel
     float* row_cache = shared;       // dim floats
@@ -286,7 +289,18 @@ __global__ void norm_accumulate_kernel(float* __restrict__ residual, const T* __
     const size_t base = static_cast<size_t>(blockIdx.x) * dim;
     float sum = 0.0f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float y = to_float(a[base + d]);
+        float y;
+        if (pair_out != nullptr) {
+            // a is the weighted sum of a row's routed experts, left un-summed: added here in the order of the choice
+            y = 0.0f;
+            for (int k = 0; k < top; ++k) {
+                const size_t pair = static_cast<size_t>(blockIdx.x) * top + k;
+                const int expert = pair_expert[pair];
+                if (expert >= 0 && expert < experts) y += pair_weight[pair] * pair_out[pair * dim + d];
+            }
+        } else {
+            y = to_float(a[base + d]);
+        }
         if (bias_a) y += bias_a[d];
         y *= scale_a;
         if (b) {
@@ -446,8 +460,10 @@ int lb_add_bias(void* x, const float* bias, int rows, int dim, int dtype, cudaSt
 // b, bias_a, bias_b and rounded may be null.
 int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, float scale_a, const void* b, const float* bias_b, float scale_b,
                        const float* weight, void* rounded, int rows, int dim, float eps, float scale_offset, int dtype, cudaStream_t stream,
-                       const float* next_weight, float next_eps, float next_offset) {
+                       const float* next_weight, float next_eps, float next_offset, const float* pair_out, const float* pair_weight,
+                       const int* pair_expert, int top, int experts) {
     if (next_weight != nullptr && rounded == nullptr) return -2;
+    if (pair_out != nullptr && (pair_weight == nullptr || pair_expert == nullptr || top < 1)) return -2;
     if (rows == 0) return 0;
     const size_t shared = (static_cast<size_t>(dim) + 33) * sizeof(float);
     if (shared > 200 * 1024) return -2;
@@ -457,7 +473,8 @@ int lb_norm_accumulate(float* residual, const void* a, const float* bias_a, floa
         auto kernel = lb::norm_accumulate_kernel<T>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         kernel<<<rows, threads, shared, stream>>>(residual, static_cast<const T*>(a), bias_a, scale_a, static_cast<const T*>(b), bias_b, scale_b, weight,
-                                                  static_cast<T*>(rounded), dim, eps, scale_offset, next_weight, next_eps, next_offset);
+                                                  static_cast<T*>(rounded), dim, eps, scale_offset, next_weight, next_eps, next_offset, pair_out, pair_weight, pair_expert, top,
+                                                  experts);
     })
     return LB_LAUNCH_RESULT();
 }

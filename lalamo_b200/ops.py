@@ -19,7 +19,7 @@ import torch
 
 from . import native
 
-__all__ = ["KernelError", "ScaledSum", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
+__all__ = ["ExpertSum", "KernelError", "ScaledSum", "SlicedSum", "dtype_code", "launch_count", "reset_launch_count"]
 
 
 class KernelError(RuntimeError):
@@ -63,9 +63,36 @@ class ScaledSum:
         """The plain tensor, in the terms' type (32-bit arithmetic, one rounding)."""
         total = None
         for tensor, scale, bias in self.terms:
+            if isinstance(tensor, ExpertSum):
+                tensor = tensor.sum()
             value = tensor.float() if bias is None else tensor.float() + bias
             total = value * scale if total is None else total + value * scale
-        return total.to(self.terms[0][0].dtype)
+        return total.to(self.terms[0][0].dtype)   # (an ExpertSum carries its dtype too)
+
+
+@dataclass
+class ExpertSum:
+    """The weighted sum of a token's routed experts left to its consumer: ``sum_k weights[t, k] * pair_out[t * top + k]`` over the
+    pairs whose expert exists, in the order of ``k`` and in 32-bit (:func:`norm_accumulate` adds them on its way; :meth:`sum`
+    gives the plain tensor in ``dtype``)."""
+
+    pair_out: torch.Tensor  # float32 [tokens * top, width]
+    weights: torch.Tensor  # float32 [tokens, top]
+    chosen: torch.Tensor  # int32 [tokens, top]
+    experts: int
+    dtype: torch.dtype
+
+    @property
+    def shape(self) -> torch.Size:
+        return torch.Size((self.chosen.shape[0], self.pair_out.shape[1]))
+
+    def sum(self) -> torch.Tensor:
+        tokens, top = self.chosen.shape
+        out = torch.empty(tokens, self.pair_out.shape[1], dtype=self.dtype, device=self.pair_out.device)
+        code = _lib().lb_moe_combine(_ptr(self.pair_out), _ptr(self.weights), _ptr(self.chosen), c_int(self.experts), _ptr(out), c_int(tokens), c_int(top),
+                                     c_int(self.pair_out.shape[1]), c_int(dtype_code(self.dtype)), _stream())
+        _done(code, "moe_combine")
+        return out
 
 
 _ACTIVATIONS = {"silu": 0, "gelu": 1, "identity": 2, "sigmoid_limit": 3}  # the last takes a `limit`, see csrc/common.cuh
@@ -258,9 +285,19 @@ def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", w
     the RMS norm of the new stream under that weight (32-bit, rounded once): what the next sublayer begins with."""
     _check(residual, "residual", torch.float32)
     _check(weight, "weight", torch.float32)
-    terms = delta.terms if isinstance(delta, ScaledSum) else [(delta, 1.0, None)]
+    terms = list(delta.terms) if isinstance(delta, ScaledSum) else [(delta, 1.0, None)]
     if not 1 <= len(terms) <= 2:
         raise KernelError("norm_accumulate: one or two terms")
+    terms = [(tensor.sum() if index > 0 and isinstance(tensor, ExpertSum) else tensor, scale, bias) for index, (tensor, scale, bias) in enumerate(terms)]
+    routed = terms[0][0] if isinstance(terms[0][0], ExpertSum) else None
+    if routed is not None:
+        # the first term comes as the experts' un-summed outputs: the kernel adds them; a stand-in of the right type and shape for the checks below
+        for name, tensor, dtype in (("pair_out", routed.pair_out, torch.float32), ("weights", routed.weights, torch.float32), ("chosen", routed.chosen, torch.int32)):
+            _check(tensor, name, dtype)
+        if routed.shape != residual.shape or routed.pair_out.shape[0] != routed.chosen.numel() or routed.weights.shape != routed.chosen.shape:
+            raise KernelError("norm_accumulate: the experts' outputs, weights and choices do not fit the residual stream")
+        stand_in = terms[1][0] if len(terms) == 2 else torch.empty(residual.shape, dtype=routed.dtype, device=residual.device)
+        terms[0] = (stand_in, terms[0][1], terms[0][2])
     first = terms[0][0]
     for tensor, _, bias in terms:
         _check(tensor, "delta", first.dtype)
@@ -284,7 +321,10 @@ def norm_accumulate(residual: torch.Tensor, delta: "torch.Tensor | ScaledSum", w
             raise KernelError("norm_accumulate: the next norm needs `rounded` and a weight of one element per column")
     code = _lib().lb_norm_accumulate(_ptr(residual), _ptr(first), _ptr(terms[0][2]), c_float(terms[0][1]), _ptr(second[0]), _ptr(second[2]), c_float(second[1]),
                                      _ptr(weight), _ptr(rounded), c_int(residual.shape[0]), c_int(residual.shape[1]), c_float(eps), c_float(scale_offset),
-                                     c_int(dtype_code(first.dtype)), _stream(), _ptr(next_weight), c_float(next_eps), c_float(next_offset))
+                                     c_int(dtype_code(first.dtype)), _stream(), _ptr(next_weight), c_float(next_eps), c_float(next_offset),
+                                     _ptr(routed.pair_out if routed is not None else None), _ptr(routed.weights if routed is not None else None),
+                                     _ptr(routed.chosen if routed is not None else None), c_int(routed.chosen.shape[1] if routed is not None else 0),
+                                     c_int(routed.experts if routed is not None else 0))
     _done(code, "norm_accumulate")
 
 
@@ -1066,12 +1106,12 @@ MOE_STREAM_MAX_PAIRS = 32  # up to this many (token, expert) pairs each pair str
 
 
 def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
-                activation: str = "silu", path: str | None = None, limit: float = 0.0) -> torch.Tensor:
+                activation: str = "silu", path: str | None = None, limit: float = 0.0, combine: bool = True) -> "torch.Tensor | ExpertSum":
     """``out[t] = sum_k weights[t, k] * down[e] (act(gate[e] x[t]) * (up[e] x[t]))`` with ``e = chosen[t, k]``;
     ``gate`` and ``up`` are ``[experts, ff, width]``, ``down`` ``[experts, width, ff]``.  The weighted sum is
     32-bit, in the order of ``k``; a pair whose expert is no expert counts nothing.  ``path`` forces one of the
     three ways the pairs' products are computed (``"grouped"``, ``"stream"``, ``"plain"``); left out, the sizes
-    choose."""
+    choose.  ``combine=False`` leaves the weighted sum to the consumer (an :class:`ExpertSum`)."""
     _check(x, "x")
     for name, tensor in (("gate", gate), ("up", up), ("down", down)):
         _check(tensor, name, x.dtype)
@@ -1117,6 +1157,8 @@ def moe_experts(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
         _done(code, "moe_expert_stream")
     else:
         raise KernelError(f"moe_experts: unknown path {path!r}")
+    if not combine:
+        return ExpertSum(pair_out, weights, chosen, experts, x.dtype)   # the consumer adds the pairs' outputs
     out = torch.empty(tokens, width, dtype=x.dtype, device=x.device)
     code = lib.lb_moe_combine(_ptr(pair_out), _ptr(weights), _ptr(chosen), c_int(experts), _ptr(out), c_int(tokens), c_int(top), c_int(width),
                               c_int(dtype_code(x.dtype)), _stream())

@@ -55,7 +55,8 @@ class RoutedMLP(FeedForward):
         spec = self.spec
         chosen, weights = ops.moe_route(x, self.router, top=spec.top, group_count=spec.group_count, group_keep=spec.group_keep, score=spec.score,
                                         renormalize=spec.renormalize, bias=self.router_bias, chosen_softmax=spec.chosen_softmax)
-        routed = ops.moe_experts(x, self.gate, self.up, self.down, chosen, weights, spec.activation, limit=spec.limit)
+        # with a shared feed-forward the consumer adds two terms anyway: the experts' weighted sum is left to it as well
+        routed = ops.moe_experts(x, self.gate, self.up, self.down, chosen, weights, spec.activation, limit=spec.limit, combine=self.shared is None)
         if self.shared is None:
             return routed
         everyone = self.shared.forward(x, step)

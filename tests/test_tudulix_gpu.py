@@ -573,3 +573,36 @@ def test_heads_products_of_the_frameworks_own(tokens, heads, k, n):
     ops.heads_product(x, w_nk, out.view(tokens, heads, n), weight_is_kn=False, gate=gate)
     want = np.einsum("thk,hnk->thn", x.double().cpu().numpy(), w_nk.double().cpu().numpy()) * plain.sigmoid(gate.double().cpu().numpy())
     assert np.abs(out.view(tokens, heads, n).float().cpu().numpy() - want).max() < 0.02 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_norm_kernel_adds_the_experts_outputs_itself(dtype):
+    """The experts' weighted sum left to the norm kernel (pairs without an expert hold NaN and count nothing) beside a second term."""
+    from lalamo_b200 import ops
+
+    generator = np.random.default_rng(31)
+    rows, dim, top, experts = 23, 200, 3, 5
+    make = lambda *shape: torch.from_numpy(generator.standard_normal(shape))
+    stream, shared = make(rows, dim).float(), make(rows, dim).to(dtype)
+    pair_out, weights = make(rows * top, dim).float(), torch.from_numpy(generator.random((rows, top))).float()
+    chosen = torch.from_numpy(generator.integers(0, experts, size=(rows, top)).astype(np.int32))
+    chosen[4, 1] = experts   # no expert
+    pair_out[4 * top + 1] = float("nan")
+    weight, following = (0.2 * make(dim)).float(), (0.2 * make(dim)).float()
+    used = pair_out.double().reshape(rows, top, dim).clone()
+    used[4, 1] = 0.0
+    routed = (weights.double()[:, :, None] * used).sum(1)
+    total = routed.numpy() + shared.double().numpy()
+    new = stream.double().numpy() + plain.offset_norm(total, weight.double().numpy(), 1e-6)
+    term = ops.ExpertSum(pair_out.cuda(), weights.cuda(), chosen.cuda(), experts, dtype)
+    device_stream = stream.cuda()
+    normed = torch.empty(rows, dim, dtype=dtype, device="cuda")
+    ops.norm_accumulate(device_stream, ops.ScaledSum([(term, 1.0, None), (shared.cuda(), 1.0, None)]), weight.cuda(), 1e-6, scale_offset=1.0, rounded=normed,
+                        next_norm=(following.cuda(), 1e-6, 1.0))
+    assert np.abs(device_stream.cpu().numpy() - new).max() < 1e-5
+    want = plain.offset_norm(new, following.double().numpy(), 1e-6)
+    assert np.abs(normed.float().cpu().numpy() - want).max() < (1e-5 if dtype == torch.float32 else 0.02)
+    # the same sum as a plain tensor, and through the two terms' plain sum
+    assert np.abs(term.sum().float().cpu().numpy() - routed.numpy()).max() < (1e-5 if dtype == torch.float32 else 0.03)
+    both = ops.ScaledSum([(term, 1.0, None), (shared.cuda(), 1.0, None)]).sum()
+    assert np.abs(both.float().cpu().numpy() - total).max() < (1e-5 if dtype == torch.float32 else 0.05)
